@@ -59,16 +59,30 @@ class LayerSpec:
 
 
 @dataclass(frozen=True)
+class StreamAdd:
+    """Something a model adds to its residual stream right before an entry of the run order runs: the embedding output
+    of the step's tokens once more (``embedding``), and/or row ``row`` of the tensor ``tensor`` (``[rows, hidden]``, a
+    learned offset for each pass of a repeated stretch of layers)."""
+
+    embedding: bool = False
+    tensor: Optional[str] = None
+    rows: int = 0
+    row: int = 0
+
+
+@dataclass(frozen=True)
 class RunEntry:
     """One position in the run order.
 
     ``layer`` indexes ``ModelSpec.layers``.  Every entry owns a cache of its own unless
     ``cache_of`` names an earlier entry (by its index in the run order): then this entry's
-    mixer reads that entry's cache and stores nothing.
+    mixer reads that entry's cache and stores nothing.  ``before`` is added to the residual
+    stream ahead of the entry.
     """
 
     layer: int
     cache_of: Optional[int] = None
+    before: Optional[StreamAdd] = None
 
 
 @dataclass

@@ -162,7 +162,7 @@ __device__ __forceinline__ bool seg_next(Seg& g, const Share& sh)
 __device__ __forceinline__ void key_range(const Params& p, const int* pos_s, int s, int& pos, int& lo)
 {
     pos = pos_s[s];
-    lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+    lo = spy_first_key(pos, p.window);
 }
 
 __device__ __forceinline__ int tiles_of(int pos, int lo) { return pos >= 0 ? pos / TILE - lo / TILE + 1 : 0; }
@@ -243,7 +243,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap page_map, const __gr
             if (blockIdx.x == 0) report_status(p.status, SPY_STATUS_BAD_POSITION, tok);
         }
         pos_s[s] = pos;
-        prefix[s + 1] = tiles_of(pos, p.window > 0 ? max(0, pos - p.window + 1) : 0);
+        prefix[s + 1] = tiles_of(pos, spy_first_key(max(pos, 0), p.window));
     }
     __syncthreads();
     if (warp == 0) {
@@ -653,7 +653,6 @@ static int run_attention_decode(const void* q, long long q_row_stride, void* out
     if (num_pages <= 0 || table_width <= 0) SPY_FAIL("attention_decode: num_pages and table_width must be positive");
     if (page_size < 8 || page_size > TILE || TILE % page_size != 0)
         SPY_FAIL("attention_decode: page_size %d must be 8, 16, 32, 64 or 128 (one TMA box per page)", page_size);
-    if (window < 0) SPY_FAIL("attention_decode: window %d must be 0 (none) or positive", window);
     if (mode < 0 || mode > 2) SPY_FAIL("attention_decode: mode %d is not 0 (the kernel decides), 1 (units split evenly) or 2 (whole pairs)", mode);
     const long long max_keys = (long long)table_width * page_size;
     if (max_keys >= (1LL << 30) || (long long)seqs * nkv * (max_keys / TILE + 1) >= (1LL << 31))

@@ -61,7 +61,7 @@ attention_generic_kernel(const TA* __restrict__ q, long long q_row_stride, TA* _
     const TA* q_row = q + (size_t)t * q_row_stride + (size_t)h * hd;
     for (int d = tid; d < hd; d += CHUNK) q_s[d] = to_f32(q_row[d]);
 
-    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int lo = spy_first_key(pos, window);
     float m = -INFINITY, l = 0.f;
     float acc[ACC];                       // dims tid, tid + 128, tid + 256, ...
 #pragma unroll
@@ -142,7 +142,6 @@ extern "C" int spy_attention_generic(const void* q, long long q_row_stride, void
     if (hd <= 0 || hd > ACC * CHUNK) SPY_FAIL("attention: head_dim %d must be positive and at most %d", hd, ACC * CHUNK);
     if (planes != 1 && planes != 2) SPY_FAIL("attention: a cache of %d planes (1: keys that are the values too, 2: keys and values)", planes);
     if (page_size <= 0 || num_pages <= 0 || table_width <= 0) SPY_FAIL("attention: page_size, num_pages and table_width must be positive");
-    if (window < 0) SPY_FAIL("attention: window %d must be 0 (none) or positive", window);
     if (nh > 65535) SPY_FAIL("attention: %d heads exceed the grid limit", nh);
     const size_t smem = (size_t)(hd + (hd & 1) + CHUNK + 33) * sizeof(float) + (size_t)CHUNK * sizeof(long long);
     dim3 grid(tokens, nh);

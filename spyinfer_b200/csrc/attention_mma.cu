@@ -436,7 +436,7 @@ __global__ void __launch_bounds__(NWARPS * 32, NWARPS <= 4 ? 2 : 1) attention_ti
     // the block's key range: its tokens are consecutive positions of one sequence
     const int block_first_pos = p.positions[block_tok0];
     const int block_last_pos = p.positions[min(tok_end, block_tok0 + tokens_per_block) - 1];
-    const int block_lo = p.window > 0 ? max(0, block_first_pos - p.window + 1) : 0;
+    const int block_lo = spy_first_key(block_first_pos, p.window);
     const int tile_first = block_lo / TILE_KEYS;
     const int n_tiles = block_last_pos / TILE_KEYS - tile_first + 1;
 
@@ -451,9 +451,9 @@ __global__ void __launch_bounds__(NWARPS * 32, NWARPS <= 4 ? 2 : 1) attention_ti
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
             row_pos[r] = row_tok[r] >= 0 ? p.positions[row_tok[r]] : -1;
-            row_lo[r] = (row_tok[r] >= 0 && p.window > 0) ? max(0, row_pos[r] - p.window + 1) : 0;
+            row_lo[r] = row_tok[r] >= 0 ? spy_first_key(row_pos[r], p.window) : 0;
         }
-        key_lo = p.window > 0 ? max(0, p.positions[tok0] - p.window + 1) : 0;
+        key_lo = spy_first_key(p.positions[tok0], p.window);
         key_hi = p.positions[min(tok_end, tok0 + tokens_per_tile) - 1];
         common_range(row_pos, row_lo, key_lo, key_hi, all_lo, all_hi);
     }
@@ -541,7 +541,7 @@ __global__ void __launch_bounds__(WARPS * 32, 2) attention_split_kernel(const Pa
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
     const int tok = p.q_start[seq];
     const int pos = p.positions[tok];
-    const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+    const int lo = spy_first_key(pos, p.window);
     const int z_first = lo / p.split_keys, z_last = pos / p.split_keys;
     if (z < z_first || z > z_last) return;
     const int key_lo = max(lo, z * p.split_keys), key_hi = min(pos, (z + 1) * p.split_keys - 1);
@@ -627,7 +627,7 @@ __global__ void attention_merge_kernel(const Params p)
     const int seq = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
     const int tok = p.q_start[seq];
     const int pos = p.positions[tok];
-    const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+    const int lo = spy_first_key(pos, p.window);
     const int z_first = lo / p.split_keys, z_last = pos / p.split_keys;
     if (z_first == z_last) return;
     const size_t base = ((size_t)tok * p.nh + head) * p.max_splits;
@@ -668,7 +668,6 @@ extern "C" int spy_attention_mma(const void* q, long long q_row_stride, void* ou
         (reinterpret_cast<uintptr_t>(out) & 15))
         SPY_FAIL("attention_mma: queries, pages and output must be 16-byte aligned with rows a multiple of 8 elements");
     if (page_size <= 0 || num_pages <= 0 || table_width <= 0) SPY_FAIL("attention_mma: page_size, num_pages and table_width must be positive");
-    if (window < 0) SPY_FAIL("attention_mma: window %d must be 0 (none) or positive", window);
     int Gp = 1;
     while (Gp < G) Gp *= 2;
     Params p;

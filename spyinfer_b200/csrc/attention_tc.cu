@@ -199,7 +199,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const __gr
             const int first_pos = p.positions[it.tok0];
             it.block_last_pos = p.positions[min(it.tok_end, it.tok0 + tokens_per_block) - 1];
             const int a_last_pos = p.positions[min(it.tok_end, it.tok0 + tokens_per_tile) - 1];
-            it.block_lo = p.window > 0 ? max(0, first_pos - p.window + 1) : 0;
+            it.block_lo = spy_first_key(first_pos, p.window);
             if (it.block_lo <= it.block_last_pos) {
                 it.tile_first = it.block_lo / TILE;
                 it.n_tiles = it.block_last_pos / TILE - it.tile_first + 1;
@@ -255,7 +255,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) attention_tc_kernel(const __gr
             const int head = kvh * p.G + hg;
             // the keys this row sees
             const int pos = row_ok ? min(p.positions[tok], it.block_last_pos) : -1;
-            const int lo = max((row_ok && p.window > 0) ? max(0, p.positions[tok] - p.window + 1) : 0, it.block_lo);
+            const int lo = max(row_ok ? spy_first_key(p.positions[tok], p.window) : 0, it.block_lo);
             if (!q_requested) request_q(it);   // the block's first item
             asm volatile("cp.async.wait_all;" ::: "memory");
             fence_async_proxy();   // the MMA reads shared memory through the async proxy
@@ -552,7 +552,6 @@ static int run_attention_tc(const void* q, long long q_row_stride, void* out, fl
         (reinterpret_cast<uintptr_t>(out) & 15))
         SPY_FAIL("attention_tc: queries, pages and output must be 16-byte aligned with rows a multiple of 8 elements");
     if (page_size <= 0 || num_pages <= 0 || table_width <= 0) SPY_FAIL("attention_tc: page_size, num_pages and table_width must be positive");
-    if (window < 0) SPY_FAIL("attention_tc: window %d must be 0 (none) or positive", window);
     const int Gp = G;   // rows a token takes in a query tile: one per head of the group (128 / G tokens a tile, the remainder of the rows stays empty)
     Params p;
     p.planes = planes;

@@ -177,6 +177,14 @@ template <typename T> __device__ __forceinline__ T from_f32(float x);
 template <> __device__ __forceinline__ float from_f32<float>(float x) { return x; }
 template <> __device__ __forceinline__ bf16 from_f32<bf16>(float x) { return __float2bfloat16_rn(x); }
 
+// The first key a query at position `pos` sees under a layer's mask: 0 = every earlier key, a positive number = the last
+// so many keys (the query's own included), a negative number -c = the keys of the query's own block of c positions,
+// blocks counted from position 0 of the sequence.
+__device__ __forceinline__ int spy_first_key(int pos, int mask)
+{
+    return mask > 0 ? max(0, pos - mask + 1) : (mask < 0 ? pos - pos % (-mask) : 0);
+}
+
 __device__ __forceinline__ void report_status(int* status, int code, int detail)
 {
     if (status != nullptr && atomicCAS(status, 0, code) == 0) status[1] = detail;

@@ -121,3 +121,45 @@ extern "C" int spy_embedding_scaled(const void* table, int table_dtype, const in
     SPY_CHECK_LAUNCH("embedding (pairs)");
     return 0;
 }
+
+// stream[t, :] += table[ids[t], :] + row[:]  (either term optional), in 32-bit: a model that adds its embedding output, or a
+// learned offset, to the residual stream again at a later point of its depth.
+template <typename TW, typename TR>
+__global__ void stream_add_kernel(float* __restrict__ stream, const TW* __restrict__ table, const int* __restrict__ ids, const TR* __restrict__ row,
+                                  int hidden, int vocab, int* status)
+{
+    pdl_enter();
+    const int t = blockIdx.x;
+    float* dst = stream + (size_t)t * hidden;
+    const TW* src = nullptr;
+    if (table != nullptr) {
+        const int id = ids[t];
+        if (id < 0 || id >= vocab) {
+            if (threadIdx.x == 0) report_status(status, SPY_STATUS_BAD_TOKEN, t);
+        } else {
+            src = table + (size_t)id * hidden;
+        }
+    }
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        float v = dst[i];
+        if (src != nullptr) v += to_f32(src[i]);
+        if (row != nullptr) v += to_f32(row[i]);
+        dst[i] = v;
+    }
+}
+
+extern "C" int spy_stream_add(float* stream, const void* table, int table_dtype, const int* ids, const void* row, int row_dtype, int tokens, int hidden,
+                              int vocab, int* status, cudaStream_t stream_)
+{
+    if (tokens <= 0 || (table == nullptr && row == nullptr)) return 0;
+    if (hidden <= 0) SPY_FAIL("stream_add: hidden %d must be positive", hidden);
+    if (table == nullptr) table_dtype = SPY_F32;
+    if (row == nullptr) row_dtype = SPY_F32;
+    SPY_DISPATCH_DTYPE(table_dtype, TW, {
+        SPY_DISPATCH_DTYPE(row_dtype, TR, {
+            spy_launch(stream_add_kernel<TW, TR>, dim3(tokens), dim3(256), 0, stream_, stream, (const TW*)table, ids, (const TR*)row, hidden, vocab, status);
+        })
+    })
+    SPY_CHECK_LAUNCH("stream_add");
+    return 0;
+}

@@ -1,0 +1,141 @@
+// Recurrences whose state is a vector (or a small matrix per channel) carried from token to token in each request's slot,
+// in 32-bit.  A step brings a run of consecutive tokens for each request; a thread owns one channel (or a share of one
+// channel's states) of one request and walks the run in order, so a token's result does not depend on where the run was cut.
+//
+// mingru_scan:  z = sigmoid(pz + bz), u = px + bx, c = u + 1/2 where u >= 0, sigmoid(u) where u < 0,
+//               S <- (1 - z) S + z c,  out = S * silu(pg)                      (element by element over `width` channels)
+// selective_scan:  dt = softplus(pdt + bdt), A = -exp(A_log); per channel c and state n
+//               S[c, n] <- exp(dt_c A[c, n]) S[c, n] + dt_c x_c B_n,  y_c = sum_n S[c, n] C_n + D_c x_c,  out = y * silu(z)
+#include "common.cuh"
+
+SPY_MODULE(spy_gated_scan)
+
+__device__ __forceinline__ float sigmoidf_(float v) { return 1.0f / (1.0f + expf(-v)); }
+
+template <typename TB, typename TO>
+__global__ void mingru_scan_kernel(const float* __restrict__ proj, long long ld, int z_col, int x_col, int g_col, const TB* __restrict__ z_bias,
+                                   const TB* __restrict__ x_bias, float* __restrict__ state, const int* __restrict__ q_start,
+                                   const int* __restrict__ state_slot, TO* __restrict__ out, int width)
+{
+    pdl_enter();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x, seq = blockIdx.y;
+    const int start = q_start[seq], end = q_start[seq + 1];
+    if (c >= width || start >= end) return;
+    float* st = state + (long long)state_slot[seq] * width + c;
+    float S = *st;
+    const float bz = z_bias != nullptr ? to_f32(z_bias[c]) : 0.f, bx = x_bias != nullptr ? to_f32(x_bias[c]) : 0.f;
+    const float* p = proj + (long long)start * ld + c;
+#pragma unroll 4
+    for (int t = start; t < end; ++t, p += ld) {
+        const float z = sigmoidf_(p[z_col] + bz);
+        const float u = p[x_col] + bx;
+        const float cand = u >= 0.f ? u + 0.5f : sigmoidf_(u);
+        const float g = p[g_col];
+        S = (1.0f - z) * S + z * cand;
+        out[(long long)t * width + c] = from_f32<TO>(S * (g * sigmoidf_(g)));
+    }
+    *st = S;
+}
+
+// proj [T, ld] float32 holds the pre-activations of z, of the candidate and of the output gate at the given columns
+// (`width` each); biases of z and the candidate or none; state [slots, width]; out [T, width].
+extern "C" int spy_mingru_scan(const float* proj, long long ld, int z_col, int x_col, int g_col, const void* z_bias, const void* x_bias, int bias_dtype,
+                               float* state, const int* q_start, const int* state_slot, int seqs, void* out, int out_dtype, int width,
+                               cudaStream_t stream)
+{
+    if (seqs <= 0) return 0;
+    if (width <= 0 || seqs > 65535) SPY_FAIL("mingru_scan: width %d, %d requests", width, seqs);
+    if (z_bias == nullptr && x_bias == nullptr) bias_dtype = SPY_F32;
+    SPY_DISPATCH_DTYPE(bias_dtype, TB, {
+        SPY_DISPATCH_DTYPE(out_dtype, TO, {
+            spy_launch(mingru_scan_kernel<TB, TO>, dim3((width + 127) / 128, seqs), dim3(128), 0, stream, proj, ld, z_col, x_col, g_col,
+                       (const TB*)z_bias, (const TB*)x_bias, state, q_start, state_slot, (TO*)out, width);
+        })
+    })
+    SPY_CHECK_LAUNCH("mingru_scan");
+    return 0;
+}
+
+constexpr int SS_PER_THREAD = 16;      // states a thread keeps in registers; a channel's states are dealt out over `lanes` threads
+
+template <typename TX, typename TW, typename TO>
+__global__ void selective_scan_kernel(const TX* __restrict__ x, const float* __restrict__ dt_pre, const TW* __restrict__ dt_bias,
+                                      const float* __restrict__ proj, long long proj_ld, int b_col, int c_col, const float* __restrict__ z,
+                                      long long z_ld, const TW* __restrict__ a_log, const TW* __restrict__ d_skip, float* __restrict__ state,
+                                      const int* __restrict__ q_start, const int* __restrict__ state_slot, TO* __restrict__ out, int inner, int n_state,
+                                      int lanes)
+{
+    pdl_enter();
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    const int c = idx / lanes, part = idx % lanes, seq = blockIdx.y;
+    const int start = q_start[seq], end = q_start[seq + 1];
+    const bool live = c < inner && start < end;          // threads past the last channel still take part in the shuffles
+    const int cc = live ? c : 0;
+    float A[SS_PER_THREAD], S[SS_PER_THREAD];
+    float* st = state + ((long long)state_slot[seq] * inner + cc) * n_state;
+#pragma unroll
+    for (int j = 0; j < SS_PER_THREAD; ++j) {
+        const int n = part + j * lanes;
+        const bool ok = live && n < n_state;
+        A[j] = ok ? -expf(to_f32(a_log[(long long)cc * n_state + n])) : 0.f;
+        S[j] = ok ? st[n] : 0.f;
+    }
+    const float bias = live ? to_f32(dt_bias[cc]) : 0.f, D = live ? to_f32(d_skip[cc]) : 0.f;
+    for (int t = start; t < end; ++t) {
+        const float pre = live ? dt_pre[(long long)t * inner + cc] + bias : 0.f;
+        const float dt = pre > 20.f ? pre : log1pf(expf(pre));
+        const float xv = live ? to_f32(x[(long long)t * inner + cc]) : 0.f;
+        const float dx = dt * xv;
+        const float* B = proj + (long long)t * proj_ld + b_col;
+        const float* C = proj + (long long)t * proj_ld + c_col;
+        float y = 0.f;
+#pragma unroll
+        for (int j = 0; j < SS_PER_THREAD; ++j) {
+            const int n = part + j * lanes;
+            if (n < n_state) {
+                S[j] = expf(dt * A[j]) * S[j] + dx * __ldg(B + n);
+                y = fmaf(S[j], __ldg(C + n), y);
+            }
+        }
+        for (int o = lanes >> 1; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
+        if (live && part == 0) {
+            y = fmaf(D, xv, y);
+            const float zv = z[(long long)t * z_ld + cc];
+            out[(long long)t * inner + cc] = from_f32<TO>(y * (zv * sigmoidf_(zv)));
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int j = 0; j < SS_PER_THREAD; ++j) {
+            const int n = part + j * lanes;
+            if (n < n_state) st[n] = S[j];
+        }
+    }
+}
+
+// x [T, inner] (after its convolution and activation), dt_pre [T, inner] float32 (the step size before its bias and softplus),
+// proj [T, proj_ld] float32 with B at b_col and C at c_col (n_state each), z [T, z_ld] float32 (first `inner` columns from the
+// pointer), a_log [inner, n_state], d_skip [inner], dt_bias [inner] of one type; state [slots, inner, n_state]; out [T, inner].
+extern "C" int spy_selective_scan(const void* x, int x_dtype, const float* dt_pre, const void* dt_bias, const float* proj, long long proj_ld, int b_col,
+                                  int c_col, const float* z, long long z_ld, const void* a_log, const void* d_skip, int weight_dtype, float* state,
+                                  const int* q_start, const int* state_slot, int seqs, void* out, int out_dtype, int inner, int n_state,
+                                  cudaStream_t stream)
+{
+    if (seqs <= 0) return 0;
+    if (inner <= 0 || n_state <= 0 || n_state > 32 * SS_PER_THREAD || seqs > 65535)
+        SPY_FAIL("selective_scan: %d channels of %d states (at most %d), %d requests", inner, n_state, 32 * SS_PER_THREAD, seqs);
+    int lanes = 1;
+    while (lanes * SS_PER_THREAD < n_state) lanes *= 2;
+    const long long threads = (long long)inner * lanes;
+    SPY_DISPATCH_DTYPE(x_dtype, TX, {
+        SPY_DISPATCH_DTYPE(weight_dtype, TW, {
+            SPY_DISPATCH_DTYPE(out_dtype, TO, {
+                spy_launch(selective_scan_kernel<TX, TW, TO>, dim3((unsigned)((threads + 127) / 128), seqs), dim3(128), 0, stream, (const TX*)x, dt_pre,
+                           (const TW*)dt_bias, proj, proj_ld, b_col, c_col, z, z_ld, (const TW*)a_log, (const TW*)d_skip, state, q_start, state_slot,
+                           (TO*)out, inner, n_state, lanes);
+            })
+        })
+    })
+    SPY_CHECK_LAUNCH("selective_scan");
+    return 0;
+}

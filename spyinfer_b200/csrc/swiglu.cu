@@ -119,3 +119,58 @@ extern "C" int spy_scale(float* x, long long total, float scale, cudaStream_t st
     SPY_CHECK_LAUNCH("scale");
     return 0;
 }
+
+// A gated activation on a fused gate|up tensor: out[t, i] = act(x[t, i]) * x[t, inter + i] in 32-bit.
+//   0: silu    1: gelu with the tanh approximation
+template <typename T>
+__global__ void gated_activation_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, long long total, int act)
+{
+    pdl_enter();
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (; i < total; i += stride) {
+        const long long row = i / inter;
+        const int col = (int)(i - row * inter);
+        const T* src = gate_up + row * 2 * inter;
+        const float g = to_f32(src[col]);
+        const float u = to_f32(src[inter + col]);
+        const float a = act == 0 ? g / (1.0f + expf(-g)) : 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+        out[i] = from_f32<T>(a * u);
+    }
+}
+
+extern "C" int spy_gated_activation(const void* gate_up, void* out, int dtype, int tokens, int inter, int act, cudaStream_t stream)
+{
+    if (tokens <= 0) return 0;
+    if (inter <= 0 || act < 0 || act > 1) SPY_FAIL("gated_activation: intermediate size %d, activation code %d", inter, act);
+    const long long total = (long long)tokens * inter;
+    long long blocks = (total + 255) / 256;
+    const long long most = (long long)spy_sm_count() * 32;
+    if (blocks > most) blocks = most;
+    SPY_DISPATCH_DTYPE(dtype, T, {
+        spy_launch(gated_activation_kernel<T>, dim3((int)blocks), dim3(256), 0, stream, (const T*)gate_up, (T*)out, inter, total, act);
+    })
+    SPY_CHECK_LAUNCH("gated_activation");
+    return 0;
+}
+
+// x[i] = cap * tanh(x[i] / cap) in place (32-bit): logits with a soft cap.
+__global__ void softcap_kernel(float* __restrict__ x, long long total, float cap)
+{
+    pdl_enter();
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (; i < total; i += stride) x[i] = cap * tanhf(x[i] / cap);
+}
+
+extern "C" int spy_softcap(float* x, long long total, float cap, cudaStream_t stream)
+{
+    if (total <= 0) return 0;
+    if (!(cap > 0.f)) SPY_FAIL("softcap: the cap %g must be positive", (double)cap);
+    long long blocks = (total + 255) / 256;
+    const long long most = (long long)spy_sm_count() * 32;
+    if (blocks > most) blocks = most;
+    spy_launch(softcap_kernel, dim3((int)blocks), dim3(256), 0, stream, x, total, cap);
+    SPY_CHECK_LAUNCH("softcap");
+    return 0;
+}

@@ -12,6 +12,7 @@ from typing import Dict, List, Optional
 
 import torch
 
+from .. import kernels
 from ..config.spec import ModelSpec
 from ..csrc import build
 from ..parts import BuildContext, build_block, build_part
@@ -47,6 +48,13 @@ class Model:
         self.layers = [_Layer(ls, self.ctx) for ls in spec.layers]
         self.final_norm = build_part(spec.final_norm, self.ctx)
         self.head = build_part(spec.head, self.ctx)
+        # tensors that the run order adds to the stream between layers (name -> rows), and the bound tensors
+        self.stream_rows: Dict[str, int] = {}
+        for e in spec.run_order:
+            if e.before is not None and e.before.tensor is not None:
+                if self.stream_rows.setdefault(e.before.tensor, e.before.rows) != e.before.rows or not 0 <= e.before.row < e.before.rows:
+                    raise ValueError(f"run order: the rows of the stream offset {e.before.tensor!r} do not agree")
+        self.stream_tensors: Dict[str, torch.Tensor] = {}
 
     # ---- weights ---------------------------------------------------------------------------
     def weight_decls(self) -> List[WeightDecl]:
@@ -54,6 +62,7 @@ class Model:
         for layer in self.layers:
             for part in layer.parts():
                 decls += _prefixed(part, layer.prefix)
+        decls += [WeightDecl(name, (rows, self.spec.hidden_size)) for name, rows in self.stream_rows.items()]
         decls += _prefixed(self.final_norm, "") + _prefixed(self.head, "")
         return decls
 
@@ -73,6 +82,7 @@ class Model:
         for layer in self.layers:
             for part in layer.parts():
                 part.bind(sub(part, layer.prefix))
+        self.stream_tensors = {name: tensors[name] for name in self.stream_rows}
         self.final_norm.bind(sub(self.final_norm, ""))
         head_names = {d.name for d in self.head.weight_decls()} | {getattr(self.head, "weight_name", None)} - {None}
         self.head.bind({n: tensors[n] for n in head_names if n in tensors})
@@ -106,6 +116,10 @@ class Model:
         mods: List[str] = []
         for part in [self.embedding, self.final_norm, self.head] + [p for l in self.layers for p in l.parts()]:
             mods += part.modules()
+        for layer in self.layers:
+            mods += list(getattr(layer.block, "kernel_modules", ()))
+        if any(e.before is not None for e in self.spec.run_order):
+            mods.append("embedding")
         return list(dict.fromkeys(mods))
 
     def graph_safe(self) -> bool:
@@ -118,7 +132,7 @@ class Model:
     def cache_needs(self):
         """Per run-order entry: its mixer's need, and the entry whose cache it reads instead."""
         cache_of = [e.cache_of for e in self.spec.run_order]
-        needs = [self.layers[e.layer].mixer.cache_need() if self.layers[e.layer].mixer is not None and e.cache_of is None else None
+        needs = [self.layers[e.layer].block.cache_need() if e.cache_of is None else None
                  for e in self.spec.run_order]               # an entry that reads another's cache keeps nothing of its own
         # what the embedding keeps between steps (a request's last token, if it looks at pairs of tokens) comes after the
         # run order's entries, as one more entry of the cache manager
@@ -133,6 +147,12 @@ class Model:
             hidden = self.embedding.forward(batch.token_ids, batch.status)
         delta = None
         for i, entry in enumerate(self.spec.run_order):
+            if entry.before is not None:
+                # the pending output of the block ahead goes in first: what is added here is added to the finished stream
+                hidden, delta = self.layers[self.spec.run_order[i - 1].layer].block.settle(hidden, delta) if i else hidden, None
+                add = entry.before
+                kernels.stream_add(hidden, self.embedding.table if add.embedding else None, batch.token_ids if add.embedding else None,
+                                   self.stream_tensors[add.tensor][add.row] if add.tensor is not None else None, batch.status)
             view = cache_manager.view(i)
             for paged in view.paged_views():
                 paged.block_table = batch.block_tables[paged.group]

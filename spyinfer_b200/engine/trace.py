@@ -46,7 +46,7 @@ def main(argv=None) -> int:
                     "count rounded up to a multiple of 64")
     ap.add_argument("--page-size", type=int, default=16, help="tokens a page (kvcache_block_size)")
     ap.add_argument("--num-pages", type=int, default=None, help="pages of the pool (num_kvcache_blocks); default: what --max-tokens needs")
-    ap.add_argument("--max-num-seqs", type=int, default=8, help="most live requests")
+    ap.add_argument("--max-num-seqs", type=int, default=4, help="most live requests (state slots)")
     args = ap.parse_args(argv)
     if (args.model is None) == (args.random is None):
         ap.error("give either --model or --random")

@@ -993,3 +993,259 @@ def wait_selftest(limit_ns: int, status: Optional[torch.Tensor] = None) -> int:
     _call("gemm_tcgen05", "spy_tcgen05_wait_selftest", ctypes.c_ulonglong(int(limit_ns)), _ptr(status), _ptr(waited), _stream())
     return int(waited.item())
 
+
+
+def group_norm(hidden: torch.Tensor, groups: int, eps: float, y: Optional[torch.Tensor] = None, y_weight: Optional[torch.Tensor] = None,
+               y_scale: float = 1.0, weight: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None,
+               write_back: bool = True) -> Optional[torch.Tensor]:
+    """RMS norm in ``groups`` equal consecutive parts of a row, around the 32-bit stream ``hidden [T, len]``.  With ``y`` (a
+    sublayer's output of hidden's shape, or a stack ``[splits, T, len]`` of partial sums) first
+    ``hidden += y_scale * group_norm(y) * y_weight`` (stored unless ``write_back`` is false or ``rows`` is given); with
+    ``weight`` and ``out [n, len]`` then ``out = group_norm(hidden) * weight``, of all rows or of the gathered ``rows``."""
+    _check(hidden, "residual stream", torch.float32, 2)
+    T, H = hidden.shape
+    yp, splits, stride = _stack_of(y, hidden, "group_norm sublayer output")
+    w_code = None
+    for w, what in ((y_weight if y is not None else None, "group_norm output weight"), (weight, "group_norm weight")):
+        if w is not None:
+            _check(w, what, ndim=1)
+            if w.shape[0] != H:
+                raise KernelError(f"{what}: {w.shape[0]} elements do not fit rows of {H}")
+            if w_code is not None and _code(w, what) != w_code:
+                raise KernelError("group_norm: the two weights differ in dtype")
+            w_code = _code(w, what)
+    if y is not None and y_weight is None:
+        raise KernelError("group_norm: a sublayer output needs its norm weight")
+    n = T
+    if rows is not None:
+        _check(rows, "group_norm rows", torch.int32, 1)
+        n = rows.shape[0]
+    if weight is not None:
+        _check(out, "group_norm output", ndim=2)
+        if tuple(out.shape) != (n, H):
+            raise KernelError(f"group_norm output: expected {(n, H)}, found {tuple(out.shape)}")
+    elif rows is not None:
+        raise KernelError("group_norm: gathered rows need a norm to go through")
+    if H % groups:
+        raise KernelError(f"group_norm: rows of {H} cannot be cut into {groups} equal groups")
+    _call("group_norm", "spy_group_norm", _ptr(hidden), _ptr(yp), _code(yp, "group_norm sublayer output") if yp is not None else 0, max(splits, 1),
+          ctypes.c_longlong(stride if splits > 1 else 0), _ptr(y_weight if y is not None else None), ctypes.c_float(y_scale), _ptr(rows),
+          _ptr(weight), w_code or 0, _ptr(out if weight is not None else None), _code(out, "group_norm output") if weight is not None else 0,
+          n, H, int(groups), ctypes.c_float(eps), int(bool(write_back and rows is None)), _stream())
+    return out
+
+
+def time_conv(x: torch.Tensor, channels: int, kernel: torch.Tensor, bias: Optional[torch.Tensor], state: Optional[torch.Tensor], q_start: torch.Tensor,
+              state_slot: torch.Tensor, num_seqs: int, longest: int, out: torch.Tensor, residual: bool = False, activation: Optional[str] = None) -> torch.Tensor:
+    """Causal convolution over time on the first ``channels`` columns of ``x [T, ld]``: ``kernel [channels, taps]`` (its last
+    column meets the current token), optional ``bias``, ``out = act(conv + bias (+ x))``.  The inputs before a request's run
+    of this step come from ``state [slots, (taps - 1) * channels]`` (float32) and the run's last ones go there.  ``longest``:
+    no request brings more tokens than this."""
+    if activation not in (None, "silu"):
+        raise KernelError(f"time_conv: unknown activation {activation!r}")
+    _check(x, "time_conv input", ndim=2)
+    _check(kernel, "time_conv kernel", ndim=2)
+    _check(out, "time_conv output", ndim=2)
+    _check(q_start, "q_start", torch.int32, 1)
+    _check(state_slot, "state_slot", torch.int32, 1)
+    taps = kernel.shape[1]
+    if kernel.shape[0] != channels or x.shape[1] < channels or out.shape[1] < channels or out.shape[0] != x.shape[0]:
+        raise KernelError(f"time_conv: input {tuple(x.shape)}, kernel {tuple(kernel.shape)}, output {tuple(out.shape)} do not fit {channels} channels")
+    if bias is not None:
+        _check(bias, "time_conv bias", kernel.dtype, 1)
+        if bias.shape[0] != channels:
+            raise KernelError("time_conv: the bias does not fit the channels")
+    if taps > 1:
+        _check(state, "time_conv state", torch.float32)
+        if state.dim() != 2 or state.shape[1] != (taps - 1) * channels:
+            raise KernelError(f"time_conv: state {tuple(state.shape)} does not fit {taps - 1} inputs of {channels} channels")
+    if q_start.shape[0] < num_seqs + 1 or state_slot.shape[0] < num_seqs:
+        raise KernelError("time_conv: q_start needs one entry per request plus one, state_slot one per request")
+    _call("time_conv", "spy_time_conv", _ptr(x), _code(x, "time_conv input"), ctypes.c_longlong(x.shape[1]), _ptr(kernel), _ptr(bias),
+          _code(kernel, "time_conv kernel"), _ptr(state if taps > 1 else None), _ptr(q_start), _ptr(state_slot), int(num_seqs), int(longest), _ptr(out),
+          _code(out, "time_conv output"), ctypes.c_longlong(out.shape[1]), int(channels), int(taps), int(bool(residual)), 1 if activation == "silu" else 0,
+          _stream())
+    return out
+
+
+def diff_qkv_store(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, bias: Optional[torch.Tensor], q_weight: torch.Tensor, k_weight: torch.Tensor,
+                   eps: float, rope_table: Optional[torch.Tensor], positions: torch.Tensor, seq_of_token: torch.Tensor, q_out: torch.Tensor,
+                   block_table: torch.Tensor, pages: torch.Tensor, heads: int, kv_heads: int, dim: int, vdim: int,
+                   status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Differential attention, the step ahead of the attention kernel.  ``proj [T, ld]`` holds, from the given columns, the
+    queries (``heads`` x two maps x ``dim``), the keys (``kv_heads`` x two maps x ``dim``) and the values (``kv_heads`` x
+    ``vdim``); ``bias [ld]`` is added.  Every map of a query or key is brought to unit root mean square over ``dim`` and
+    multiplied by ``q_weight`` / ``k_weight [dim]``, its pairs ``(2i, 2i + 1)`` rotated by ``rope_table [positions, r, 2]``.
+    ``q_out [T, 2 heads, hd]`` gets each map as a query head with zeros in the other map's columns;
+    ``pages [num_pages, 2, kv_heads, page_size, hd]`` get the key rows ``[map 1 | map 2]`` and the values."""
+    _check(proj, "projection", ndim=2)
+    _check(q_out, "queries", ndim=2)
+    _check(pages, "cache pages", q_out.dtype, 5)
+    _check(block_table, "block table", torch.int32, 2)
+    _check(positions, "positions", torch.int32, 1)
+    _check(seq_of_token, "seq_of_token", torch.int32, 1)
+    _check(q_weight, "q norm weight", ndim=1)
+    _check(k_weight, "k norm weight", q_weight.dtype, 1)
+    T, ld = proj.shape
+    num_pages, two, nkv, page_size, hd = pages.shape
+    if two != 2 or nkv != kv_heads or tuple(q_out.shape) != (T, 2 * heads * hd) or positions.shape[0] != T or seq_of_token.shape[0] != T:
+        raise KernelError(f"diff_qkv_store: pages {tuple(pages.shape)} / queries {tuple(q_out.shape)} do not fit {heads} heads over {kv_heads} of rows {hd}")
+    if max(q_col + 2 * heads * dim, k_col + 2 * kv_heads * dim, v_col + kv_heads * vdim) > ld or q_weight.shape[0] != dim or k_weight.shape[0] != dim:
+        raise KernelError("diff_qkv_store: the columns or the norm weights do not fit the projection")
+    if bias is not None:
+        _check(bias, "projection bias", ndim=1)
+        if bias.shape[0] != ld:
+            raise KernelError("diff_qkv_store: the bias has one entry per column of the projection")
+    rot_half = table_rows = 0
+    if rope_table is not None:
+        _check(rope_table, "rope table", torch.float32, 3)
+        table_rows, rot_half = rope_table.shape[0], rope_table.shape[1]
+    _call("diff_attention", "spy_diff_qkv_store", _ptr(proj), _code(proj, "projection"), ctypes.c_longlong(ld), int(q_col), int(k_col), int(v_col), _ptr(bias),
+          _code(bias, "projection bias") if bias is not None else 0, _ptr(q_weight), _ptr(k_weight), _code(q_weight, "q norm weight"), ctypes.c_float(eps),
+          _ptr(rope_table), rot_half, table_rows, _ptr(positions), _ptr(seq_of_token), _ptr(q_out), _code(q_out, "queries"), _ptr(block_table),
+          block_table.shape[1], _ptr(pages), _code(pages, "cache pages"), page_size, num_pages, T, int(heads), int(kv_heads), int(dim), int(vdim), hd,
+          _ptr(status), _stream())
+    return q_out
+
+
+def diff_combine(attn: torch.Tensor, hd: int, gate: Optional[torch.Tensor], gate_col: int, out: torch.Tensor, heads: int, vdim: int, lam: float,
+                 post: float, eps: float) -> torch.Tensor:
+    """``out[t, h] = unit_rms(a1 - lam * a2) * post * sigmoid(gate[t, gate_col + h vdim ...])`` with ``a1``, ``a2`` the first
+    ``vdim`` elements of the rows ``2h`` and ``2h + 1`` of ``attn [T, 2 heads * hd]``; ``out [T, heads * vdim]``."""
+    _check(attn, "attention result", ndim=2)
+    _check(out, "combined heads", ndim=2)
+    T = attn.shape[0]
+    if attn.shape[1] != 2 * heads * hd or tuple(out.shape) != (T, heads * vdim):
+        raise KernelError(f"diff_combine: result {tuple(attn.shape)} / output {tuple(out.shape)} do not fit {heads} heads of {vdim} in rows of {hd}")
+    gate_ld = 0
+    if gate is not None:
+        _check(gate, "gate", ndim=2)
+        gate_ld = gate.shape[1]
+        if gate.shape[0] != T or gate_col < 0 or gate_col + heads * vdim > gate_ld:
+            raise KernelError("diff_combine: the gate's columns do not fit")
+    _call("diff_attention", "spy_diff_combine", _ptr(attn), _code(attn, "attention result"), int(hd), _ptr(gate), _code(gate, "gate") if gate is not None else 0,
+          ctypes.c_longlong(gate_ld), int(gate_col), _ptr(out), _code(out, "combined heads"), T, int(heads), int(vdim), ctypes.c_float(lam),
+          ctypes.c_float(post), ctypes.c_float(eps), _stream())
+    return out
+
+
+def mingru_scan(proj: torch.Tensor, z_col: int, x_col: int, g_col: int, z_bias: Optional[torch.Tensor], x_bias: Optional[torch.Tensor], state: torch.Tensor,
+                q_start: torch.Tensor, state_slot: torch.Tensor, num_seqs: int, out: torch.Tensor, width: int) -> torch.Tensor:
+    """``S <- (1 - z) S + z c`` element by element over every request's tokens of this step, from and into ``state [slots, width]``;
+    ``z = sigmoid(proj[:, z_col..] + z_bias)``, ``u = proj[:, x_col..] + x_bias``, ``c = u + 1/2`` where ``u >= 0`` else
+    ``sigmoid(u)``; ``out = S * silu(proj[:, g_col..])``.  ``proj`` float32."""
+    _check(proj, "fused projection", torch.float32, 2)
+    _check(state, "recurrent state", torch.float32, 2)
+    _check(out, "recurrence output", ndim=2)
+    _check(q_start, "q_start", torch.int32, 1)
+    _check(state_slot, "state_slot", torch.int32, 1)
+    if max(z_col, x_col, g_col) + width > proj.shape[1] or state.shape[1] != width or tuple(out.shape) != (proj.shape[0], width):
+        raise KernelError("mingru_scan: the columns, the state or the output do not fit")
+    for b in (z_bias, x_bias):
+        if b is not None:
+            _check(b, "gate bias", ndim=1)
+            if b.shape[0] != width or (z_bias is not None and b.dtype != z_bias.dtype):
+                raise KernelError("mingru_scan: the biases have one entry per channel and one dtype")
+    some = z_bias if z_bias is not None else x_bias
+    _call("gated_scan", "spy_mingru_scan", _ptr(proj), ctypes.c_longlong(proj.shape[1]), int(z_col), int(x_col), int(g_col), _ptr(z_bias), _ptr(x_bias),
+          _code(some, "gate bias") if some is not None else 0, _ptr(state), _ptr(q_start), _ptr(state_slot), int(num_seqs), _ptr(out),
+          _code(out, "recurrence output"), int(width), _stream())
+    return out
+
+
+def selective_scan(x: torch.Tensor, dt_pre: torch.Tensor, dt_bias: torch.Tensor, proj: torch.Tensor, b_col: int, c_col: int, z: torch.Tensor, z_col: int,
+                   a_log: torch.Tensor, d_skip: torch.Tensor, state: torch.Tensor, q_start: torch.Tensor, state_slot: torch.Tensor, num_seqs: int,
+                   out: torch.Tensor) -> torch.Tensor:
+    """The selective scan over every request's tokens of this step, from and into ``state [slots, inner * n]``:
+    ``dt = softplus(dt_pre + dt_bias)``, ``S[c, n] <- exp(-dt_c exp(a_log[c, n])) S[c, n] + dt_c x_c B_n``,
+    ``y_c = sum_n S[c, n] C_n + d_skip_c x_c``, ``out = y * silu(z)``.  ``x [T, inner]``; ``dt_pre [T, inner]`` float32;
+    ``proj`` float32 holds ``B`` and ``C`` (``n`` columns each) at ``b_col`` and ``c_col``; ``z`` float32 holds the gate's
+    ``inner`` columns from ``z_col``."""
+    _check(x, "scan input", ndim=2)
+    T, inner = x.shape
+    _check(dt_pre, "step size pre-activation", torch.float32, 2)
+    _check(proj, "B and C", torch.float32, 2)
+    _check(z, "gate", torch.float32, 2)
+    _check(a_log, "A_log", ndim=2)
+    _check(dt_bias, "step size bias", a_log.dtype, 1)
+    _check(d_skip, "D", a_log.dtype, 1)
+    _check(state, "recurrent state", torch.float32, 2)
+    _check(out, "scan output", ndim=2)
+    n = a_log.shape[1]
+    if (tuple(dt_pre.shape) != (T, inner) or a_log.shape[0] != inner or dt_bias.shape[0] != inner or d_skip.shape[0] != inner or state.shape[1] != inner * n
+            or tuple(out.shape) != (T, inner) or max(b_col, c_col) + n > proj.shape[1] or proj.shape[0] != T or z.shape[0] != T or z_col + inner > z.shape[1]):
+        raise KernelError("selective_scan: shapes do not fit")
+    z_view_ptr = ctypes.c_void_p(z.data_ptr() + 4 * z_col)
+    _call("gated_scan", "spy_selective_scan", _ptr(x), _code(x, "scan input"), _ptr(dt_pre), _ptr(dt_bias), _ptr(proj), ctypes.c_longlong(proj.shape[1]),
+          int(b_col), int(c_col), z_view_ptr, ctypes.c_longlong(z.shape[1]), _ptr(a_log), _ptr(d_skip), _code(a_log, "A_log"), _ptr(state), _ptr(q_start),
+          _ptr(state_slot), int(num_seqs), _ptr(out), _code(out, "scan output"), inner, n, _stream())
+    return out
+
+
+def moe_activation(gate_up: torch.Tensor, logits: torch.Tensor, out: torch.Tensor, experts: int, top: int, ff: int, limit: float, shared_ff: int = 0,
+                   shared_limit: float = 0.0, alpha: float = 1.702, weights_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Routing weights and expert activations of a mixture of experts in one pass.  ``logits [T, >= experts (+ 1)]`` float32:
+    the router's logits and, with a shared expert, its gate's logit behind them.  ``gate_up [T, 2 (experts ff + shared_ff)]``:
+    per expert ``[gate | up]``, the shared expert last.  ``out [T, experts ff + shared_ff]`` gets, per expert,
+    ``weight * g * sigmoid(alpha g) * (u + 1)`` with ``g = min(gate, limit)``, ``u = clamp(up, -limit, limit)``; the weight is the
+    expert's softmax score if it is among the token's ``top`` largest, else 0, and ``sigmoid`` of its logit for the shared expert."""
+    _check(gate_up, "expert gate|up", ndim=2)
+    _check(logits, "router logits", torch.float32, 2)
+    _check(out, "expert activations", ndim=2)
+    T = gate_up.shape[0]
+    cols = experts * ff + shared_ff
+    if gate_up.shape[1] != 2 * cols or tuple(out.shape) != (T, cols) or logits.shape[0] != T or logits.shape[1] < experts + (1 if shared_ff else 0):
+        raise KernelError(f"moe_activation: gate|up {tuple(gate_up.shape)}, logits {tuple(logits.shape)}, output {tuple(out.shape)} do not fit")
+    if weights_out is not None:
+        _check(weights_out, "routing weights", torch.float32, 2)
+        if tuple(weights_out.shape) != (T, experts + 1):
+            raise KernelError("moe_activation: the routing weights are [T, experts + 1]")
+    _call("moe", "spy_moe_activation", _ptr(gate_up), _code(gate_up, "expert gate|up"), ctypes.c_longlong(gate_up.shape[1]), _ptr(logits),
+          ctypes.c_longlong(logits.shape[1]), _ptr(out), _code(out, "expert activations"), ctypes.c_longlong(out.shape[1]), T, int(experts), int(top),
+          int(ff), ctypes.c_float(limit), int(shared_ff), ctypes.c_float(shared_limit), ctypes.c_float(alpha), _ptr(weights_out), _stream())
+    return out
+
+
+_GATED_ACTIVATIONS = ("silu", "gelu_tanh")
+
+
+def gated_activation(gate_up: torch.Tensor, out: torch.Tensor, kind: str) -> torch.Tensor:
+    """``out[t, i] = act(gate_up[t, i]) * gate_up[t, I + i]``; ``kind``: ``silu`` or ``gelu_tanh``."""
+    if kind not in _GATED_ACTIVATIONS:
+        raise KernelError(f"gated_activation: unknown kind {kind!r}")
+    _check(gate_up, "gated activation input", ndim=2)
+    _check(out, "gated activation output", gate_up.dtype, 2)
+    T, two_i = gate_up.shape
+    if two_i % 2 != 0 or tuple(out.shape) != (T, two_i // 2):
+        raise KernelError(f"gated_activation: input {tuple(gate_up.shape)} and output {tuple(out.shape)} do not fit")
+    _call("swiglu", "spy_gated_activation", _ptr(gate_up), _ptr(out), _code(gate_up, "gated activation input"), T, two_i // 2,
+          _GATED_ACTIVATIONS.index(kind), _stream())
+    return out
+
+
+def softcap_(x: torch.Tensor, cap: float) -> torch.Tensor:
+    """``x = cap * tanh(x / cap)`` in place; x float32."""
+    _check(x, "capped tensor", torch.float32)
+    _call("swiglu", "spy_softcap", _ptr(x), ctypes.c_longlong(x.numel()), ctypes.c_float(cap), _stream())
+    return x
+
+
+def stream_add(stream: torch.Tensor, table: Optional[torch.Tensor], ids: Optional[torch.Tensor], row: Optional[torch.Tensor],
+               status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``stream[t] += table[ids[t]] + row`` in place (either term optional); stream float32 ``[T, H]``."""
+    _check(stream, "residual stream", torch.float32, 2)
+    T, H = stream.shape
+    V = 0
+    if table is not None:
+        _check(table, "embedding table", ndim=2)
+        _check(ids, "token ids", torch.int32, 1)
+        V = table.shape[0]
+        if table.shape[1] != H or ids.shape[0] != T:
+            raise KernelError("stream_add: the table's rows and the token ids must fit the stream")
+    if row is not None:
+        _check(row, "offset row", ndim=1)
+        if row.shape[0] != H:
+            raise KernelError("stream_add: the offset row must have the stream's width")
+    _call("embedding", "spy_stream_add", _ptr(stream), _ptr(table), _code(table, "embedding table") if table is not None else 0, _ptr(ids), _ptr(row),
+          _code(row, "offset row") if row is not None else 0, T, H, V, _ptr(status), _stream())
+    return stream

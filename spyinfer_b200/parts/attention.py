@@ -26,8 +26,9 @@ from .registry import build_part, register_part
 class Attention(Mixer):
     """params: ``hidden_size``, ``num_heads``, ``num_kv_heads``, ``head_dim``, ``qk_norm_eps``
     (None: no q/k norm), ``position`` (a PartSpec or None), ``window`` (None: all keys),
-    ``scale`` (None: 1/sqrt(head_dim)), ``prefix``, ``qkv_bias`` and ``o_bias`` (default false: the
-    projections have bias tensors ``{q,k,v}_proj.bias`` / ``o_proj.bias``)."""
+    ``chunk`` (None, or a size: a query sees the earlier keys of its own block of that many positions only, blocks counted
+    from position 0 of the sequence; not together with a window), ``scale`` (None: 1/sqrt(head_dim)), ``prefix``,
+    ``qkv_bias`` and ``o_bias`` (default false: the projections have bias tensors ``{q,k,v}_proj.bias`` / ``o_proj.bias``)."""
 
     graph_safe = True
     #: False: the head size must be a multiple of 4 (the kernel that rotates and stores q, k and v reads quads)
@@ -45,6 +46,9 @@ class Attention(Mixer):
         self.window = params.get("window")
         if self.window is not None and int(self.window) <= 0:
             raise ValueError(f"attention: window {self.window} must be positive")
+        self.chunk = params.get("chunk")
+        if self.chunk is not None and (int(self.chunk) <= 0 or self.window is not None):
+            raise ValueError(f"attention: chunk {self.chunk} must be positive, and a layer has a window or chunks, not both")
         self.scale = float(params["scale"]) if params.get("scale") is not None else 1.0 / math.sqrt(float(self.hd))
         self.prefix = params.get("prefix", "")
         self.qkv_bias, self.o_bias = bool(params.get("qkv_bias", False)), bool(params.get("o_bias", False))
@@ -96,6 +100,11 @@ class Attention(Mixer):
     def cache_need(self):
         return PagedCacheNeed(self.nkv, self.hd, int(self.window) if self.window is not None else None)
 
+    @property
+    def key_mask(self):
+        """What the attention kernels take as ``window``: None (every earlier key), the window, or minus the chunk size."""
+        return -int(self.chunk) if self.chunk is not None else self.window
+
     def split_plan(self, num_seqs: int):
         """(split_keys, max_splits) for decoding ``num_seqs`` requests: the keys of every request
         are cut into ranges so that (requests x key/value heads x ranges) blocks fill whole waves
@@ -144,12 +153,12 @@ class Attention(Mixer):
                 and kernels.attention_decode_takes(self.nh, self.nkv, self.hd, cache.page_size, x.dtype)):
             # memory-bound: one persistent block per SM, the batch's key tiles shared out evenly, pages by TMA
             kernels.attention_decode(q, self.nh, self.hd, out, cache.pages, cache.block_table, batch.positions, batch.q_start,
-                                     batch.num_seqs, self.scale, window=self.window, status=batch.status)
+                                     batch.num_seqs, self.scale, window=self.key_mask, status=batch.status)
         elif decoding and self.mma:
             # page sizes that are no TMA box, or very many requests: keys split across blocks by a plan per batch size
             split_keys, max_splits = self.split_plan(batch.num_seqs)
             kernels.attention_mma(q, self.nh, self.hd, out, cache.pages, cache.block_table, batch.positions, batch.q_start,
-                                  batch.num_seqs, self.scale, window=self.window, split_keys=split_keys, max_splits=max_splits,
+                                  batch.num_seqs, self.scale, window=self.key_mask, split_keys=split_keys, max_splits=max_splits,
                                   status=batch.status)
         elif boxes:
             # prompt portions on blocks of 256 query rows; requests that decode beside them (laid out first in the batch)
@@ -160,16 +169,16 @@ class Attention(Mixer):
                 head = 0
             if head:
                 kernels.attention_decode(q, self.nh, self.hd, out, cache.pages, cache.block_table[:head], batch.positions, batch.q_start[:head + 1],
-                                         head, self.scale, window=self.window, status=batch.status)
+                                         head, self.scale, window=self.key_mask, status=batch.status)
             kernels.attention_tc(q, self.nh, self.hd, out, cache.pages, cache.block_table[head:], batch.positions, batch.q_start[head:],
-                                 batch.num_seqs - head, self.scale, window=self.window, status=batch.status)
+                                 batch.num_seqs - head, self.scale, window=self.key_mask, status=batch.status)
         elif self.mma:
             kernels.attention_mma(q, self.nh, self.hd, out, cache.pages, cache.block_table, batch.positions, batch.q_start,
-                                  batch.num_seqs, self.scale, window=self.window, status=batch.status)
+                                  batch.num_seqs, self.scale, window=self.key_mask, status=batch.status)
         else:
             # the float32 path, head sizes above 128 or no multiple of 8, more than 16 query heads a key/value head
             kernels.attention_generic(q, self.nh, self.hd, out, cache.pages, cache.block_table, batch.positions, batch.seq_of_token,
-                                      self.scale, window=self.window, status=batch.status)
+                                      self.scale, window=self.key_mask, status=batch.status)
         return out
 
 
@@ -377,3 +386,93 @@ class LatentAttention(Attention):
         o = torch.empty((T, H * self.vd), dtype=x.dtype, device=x.device)
         kernels.head_product(mixed, self.width, self.uv, o, self.vd, gate=fused if self.gated else None, gate_offset=self.gate_offset)
         return self.o(o, defer=self.defer_output)
+
+
+@register_part("differential_attention")
+class DifferentialAttention(Attention):
+    """Softmax attention with two score maps a head over the same values, the second map's result subtracted from the
+    first's: with ``a1``, ``a2`` the two maps' results, ``o = a1 - lambda * a2``, brought to unit root mean square over the
+    head's values (no weight) and multiplied by ``1 - diff``; ``lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff`` is one
+    number for the layer.  Queries and keys are laid out head by head as ``[map 1 | map 2]``; each map of each head gets an
+    RMS norm over ``dim`` with a weight shared by all heads and maps, then the rotation.  The concatenated heads are
+    multiplied by ``sigmoid(W_g h)`` ahead of the output projection.  q, k, v and o have biases.
+
+    The two maps run as two query heads of the ordinary attention kernels over one key/value head whose key row is
+    ``[key of map 1 | key of map 2]`` and whose query has zeros in the other map's columns (``csrc/diff_attention.cu``): the
+    kernels see ``2 heads`` query heads over ``kv_heads`` key/value heads of rows ``max(2 dim, vdim)`` wide, rounded up to 8.
+
+    params: ``hidden_size``, ``heads``, ``kv_heads``, ``dim`` (a map's query/key size), ``vdim``, ``diff``, ``scale``
+    (None: ``dim^(-1/2)``), ``eps`` (of the norms), ``window`` or ``chunk`` (as ``attention``), ``position`` (a rotary part
+    with the interleaved pairing, or None), ``prefix``.  Tensors: ``q [2 heads dim, hidden]``, ``k [2 kv_heads dim, hidden]``,
+    ``v [kv_heads vdim, hidden]`` with biases ``q.b, k.b, v.b``, ``q.norm, k.norm, lq1, lk1, lq2, lk2 [dim]``,
+    ``g [heads vdim, hidden]``, ``o [hidden, heads vdim]``, ``o.b``."""
+
+    graph_safe = True
+    any_head_dim = True
+
+    def __init__(self, params, ctx):
+        self.heads, self.groups = int(params["heads"]), int(params["kv_heads"])
+        self.d, self.vd, self.diff, self.eps = int(params["dim"]), int(params["vdim"]), float(params["diff"]), float(params["eps"])
+        if min(self.heads, self.groups, self.d, self.vd) <= 0:
+            raise ValueError("differential_attention: sizes must be positive")
+        row = (max(2 * self.d, self.vd) + 7) // 8 * 8
+        base = dict(params)
+        base.update(num_heads=2 * self.heads, num_kv_heads=self.groups, head_dim=row, qk_norm_eps=None)
+        if base.get("scale") is None:
+            base["scale"] = 1.0 / math.sqrt(float(self.d))
+        super().__init__(base, ctx)
+        if self.position is not None and (self.position.pairing != "interleaved" or self.position.rotary_dim > self.d):
+            raise ValueError("differential_attention: the rotation pairs neighbouring elements and fits within a map")
+        n_q, n_k, n_v = 2 * self.heads * self.d, 2 * self.groups * self.d, self.groups * self.vd
+        self.cols = (0, n_q, n_q + n_k, n_q + n_k + n_v)          # q, k, v, gate in the fused projection
+        self.fused = self.o = self.bias = self.q_norm_w = self.k_norm_w = None
+        self.lam = 0.0
+
+    def weight_decls(self):
+        p, H, G, d, vd, W = self.prefix, self.heads, self.groups, self.d, self.vd, self.hidden
+        return ([WeightDecl(p + "q", (2 * H * d, W)), WeightDecl(p + "q.b", (2 * H * d,)), WeightDecl(p + "k", (2 * G * d, W)),
+                 WeightDecl(p + "k.b", (2 * G * d,)), WeightDecl(p + "v", (G * vd, W)), WeightDecl(p + "v.b", (G * vd,)),
+                 WeightDecl(p + "q.norm", (d,), init="one_plus_normal"), WeightDecl(p + "k.norm", (d,), init="one_plus_normal")]
+                + [WeightDecl(p + n, (d,)) for n in ("lq1", "lk1", "lq2", "lk2")]
+                + [WeightDecl(p + "g", (H * vd, W)), WeightDecl(p + "o", (W, H * vd)), WeightDecl(p + "o.b", (W,))])
+
+    def bind(self, tensors):
+        p = self.prefix
+        rows = [tensors[p + n] for n in ("q", "k", "v", "g")]
+        if len({t.dtype for t in rows}) > 1:
+            rows = [t.float() for t in rows]
+        self.fused = Linear(torch.cat(rows, dim=0).contiguous(), self.ctx.dtype)
+        self.bias = torch.cat([tensors[p + n].float() for n in ("q.b", "k.b", "v.b")]
+                              + [torch.zeros(self.heads * self.vd, dtype=torch.float32, device=rows[0].device)]).contiguous()
+        self.o = Linear(tensors[p + "o"], self.ctx.dtype, bias=tensors[p + "o.b"])
+        self.q_norm_w, self.k_norm_w = tensors[p + "q.norm"].float().contiguous(), tensors[p + "k.norm"].float().contiguous()
+        l = [tensors[p + n].double() for n in ("lq1", "lk1", "lq2", "lk2")]
+        self.lam = float(torch.exp((l[0] * l[1]).sum()) - torch.exp((l[2] * l[3]).sum())) + self.diff
+
+    def modules(self):
+        mods = (["diff_attention"] + (["attention_tc", "attention_decode"] if self.tc else []) + (["attention_mma"] if self.mma else ["attention_generic"])
+                + self.fused.modules() + self.o.modules())
+        if self.position is not None:
+            mods += self.position.modules()
+        return mods
+
+    def linears(self):
+        return [self.fused, self.o]
+
+    def cache_need(self):
+        return PagedCacheNeed(self.groups, self.hd, int(self.window) if self.window is not None else None)
+
+    def forward(self, x, batch, cache):
+        if self.rope_table is None and self.position is not None:
+            self.rope_table = self.position.rotation_table()
+        T = x.shape[0]
+        proj = self.fused(x, out_dtype=torch.float32)
+        q = torch.empty((T, self.nh * self.hd), dtype=x.dtype, device=x.device)
+        kernels.diff_qkv_store(proj, self.cols[0], self.cols[1], self.cols[2], self.bias, self.q_norm_w, self.k_norm_w, self.eps, self.rope_table,
+                               batch.positions, batch.seq_of_token, q, cache.block_table, cache.pages, self.heads, self.groups, self.d, self.vd,
+                               status=batch.status)
+        maps = torch.empty((T, self.nh * self.hd), dtype=x.dtype, device=x.device)
+        self.attend(q, maps, batch, cache)
+        o = torch.empty((T, self.heads * self.vd), dtype=x.dtype, device=x.device)
+        kernels.diff_combine(maps, self.hd, proj, self.cols[3], o, self.heads, self.vd, self.lam, 1.0 - self.diff, self.eps)
+        return self.o(o, defer=self.defer_output, out_dtype=self.output_dtype)

@@ -43,6 +43,17 @@ class ScaledParts:
     terms: List[Tuple[torch.Tensor, float]]
 
 
+@dataclass
+class NormedDelta:
+    """A sublayer output that is still to be normed, weighted and added: ``residual += scale * norm(y) * weight``, the norm
+    being that of the part which made this record (and which the next norm of the same kind folds into its own launch).
+    ``y`` is ``[rows, size]`` or a stack ``[splits, rows, size]`` of float32 partial products."""
+
+    y: torch.Tensor
+    weight: torch.Tensor
+    scale: float = 1.0
+
+
 class Part:
     kind: str = ""
     #: kernel modules (``csrc/<name>.cu``) this part launches; built before the first step
@@ -157,3 +168,16 @@ class Block:
         """``hidden`` is the 32-bit residual stream; ``delta`` the previous block's output
         that is still to be added to it (None for the first).  Returns the same pair."""
         raise NotImplementedError
+
+    def cache_need(self):
+        """What the layer keeps between steps: its mixer's need, unless the arrangement keeps something of its own beside
+        it (it then returns a ``CompositeCacheNeed`` and hands the mixer its part of the view)."""
+        mixer = self.parts.get("mixer")
+        return mixer.cache_need() if mixer is not None else None
+
+    def settle(self, hidden: torch.Tensor, delta):
+        """Adds what ``forward`` left pending to the stream (the model asks for this when something else is added to the
+        stream between two blocks).  Returns the stream."""
+        if delta is None:
+            return hidden
+        raise NotImplementedError(f"block arrangement {self.kind!r} cannot add its pending output to the stream on its own")

@@ -112,3 +112,61 @@ class ScaledPreNormBlock(Block):
             return hidden, a
         x = self.ffn_norm.forward_add(hidden, a, scale=self.residual_scale)
         return hidden, self.feed_forward.forward(x)
+
+
+@register_block("sandwich_norm")
+class SandwichNormBlock(Block):
+    """``h += m * out_norm(mixer(c(norm(h))))`` and the same around the feed-forward: a norm on both sides of every sublayer,
+    one multiplier ``m`` (param ``residual_scale``) on what the stream takes, and optionally an input convolution ``c`` over
+    time (a part that offers ``forward(x, batch, cache)`` and ``cache_need()``, such as ``causal_conv``) between the first
+    norm and the sublayer.  A layer may do without the feed-forward half.
+
+    The output norms must offer ``defer``/``add_normed`` (``group_rms_norm``): a sublayer's output is handed on as a record
+    that the next norm of the stream adds, normed and weighted, in the launch that also norms the stream for the next
+    sublayer.  What the convolutions keep between steps lies beside the mixer's cache: the layer's need is a composite of
+    (the mixer convolution's state, the feed-forward convolution's state, the mixer's need), parts that are absent left out."""
+
+    graph_safe = True
+    required = ("mixer_norm", "mixer", "mixer_out_norm")
+    optional = ("mixer_conv", "ffn_norm", "ffn_conv", "feed_forward", "ffn_out_norm")
+
+    def __init__(self, parts, params=None):
+        super().__init__(parts, params)
+        self.mult = float(self.params.get("residual_scale", 1.0))
+        if len({self.ffn_norm is None, self.feed_forward is None, self.ffn_out_norm is None}) > 1:
+            raise ValueError("block arrangement 'sandwich_norm': the feed-forward and its two norms come together or not at all")
+        if self.ffn_conv is not None and self.feed_forward is None:
+            raise ValueError("block arrangement 'sandwich_norm': an input convolution of the feed-forward needs the feed-forward")
+        for norm in (self.mixer_out_norm, self.ffn_out_norm):
+            if norm is not None and not (hasattr(norm, "defer") and hasattr(norm, "add_normed")):
+                raise ValueError(f"block arrangement 'sandwich_norm': the norm {norm.kind!r} cannot hand a normed output on to the stream")
+        self.mixer.output_dtype = torch.float32      # what an output norm reads is not rounded to 16 bits first
+        # where each holder of state finds its view among the parts of the layer's composite need
+        self._order = [role for role in ("mixer_conv", "ffn_conv", "mixer") if self.parts.get(role) is not None and self.parts[role].cache_need() is not None]
+
+    def cache_need(self):
+        from ..config.spec import CompositeCacheNeed
+        needs = tuple(self.parts[role].cache_need() for role in self._order)
+        if self._order == ["mixer"]:
+            return needs[0]
+        return CompositeCacheNeed(needs) if needs else None
+
+    def _view(self, cache, role):
+        if role not in self._order:
+            return None
+        return cache if self._order == ["mixer"] else cache.parts[self._order.index(role)]
+
+    def forward(self, hidden, delta, batch, cache):
+        x = self.mixer_norm.forward_add(hidden, delta)
+        if self.mixer_conv is not None:
+            x = self.mixer_conv.forward(x, batch, self._view(cache, "mixer_conv"))
+        delta = self.mixer_out_norm.defer(self.mixer.forward(x, batch, self._view(cache, "mixer")), self.mult)
+        if self.feed_forward is None:
+            return hidden, delta
+        x = self.ffn_norm.forward_add(hidden, delta)
+        if self.ffn_conv is not None:
+            x = self.ffn_conv.forward(x, batch, self._view(cache, "ffn_conv"))
+        return hidden, self.ffn_out_norm.defer(self.feed_forward.forward(x), self.mult)
+
+    def settle(self, hidden, delta):
+        return self.mixer_out_norm.add_normed(hidden, delta) if delta is not None else hidden

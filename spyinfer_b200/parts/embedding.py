@@ -66,7 +66,8 @@ class TokenEmbedding(Part):
 class LMHead(Part):
     graph_safe = True
     """params: ``vocab_size``, ``hidden_size``, ``tied``, ``weight`` (full name when untied),
-    ``tied_to`` (full name of the embedding table when tied), ``scale`` (default 1: the logits' multiplier)."""
+    ``tied_to`` (full name of the embedding table when tied), ``scale`` (default 1: the logits' multiplier), ``softcap``
+    (default 0: none; else ``logits = cap * tanh(logits / cap)``, after the scale)."""
 
     def __init__(self, params, ctx):
         super().__init__(params, ctx)
@@ -74,6 +75,9 @@ class LMHead(Part):
         self.weight_name = params["tied_to"] if self.tied else params["weight"]
         self.ignorable = [params["weight"]] if self.tied else []
         self.scale = float(params.get("scale", 1.0))
+        self.softcap = float(params.get("softcap") or 0.0)
+        if self.softcap < 0.0:
+            raise ValueError(f"lm_head: the logits' cap {self.softcap} must not be negative")
         self.linear = None
 
     def weight_decls(self):
@@ -83,11 +87,13 @@ class LMHead(Part):
         self.linear = Linear(tensors[self.weight_name], self.ctx.dtype)
 
     def modules(self):
-        return self.linear.modules() + (["swiglu"] if self.scale != 1.0 else [])
+        return self.linear.modules() + (["swiglu"] if self.scale != 1.0 or self.softcap else [])
 
     def linears(self):
         return [self.linear]
 
     def forward(self, x):
         logits = self.linear(x, out_dtype=torch.float32)
-        return kernels.scale_(logits, self.scale) if self.scale != 1.0 else logits
+        if self.scale != 1.0:
+            kernels.scale_(logits, self.scale)
+        return kernels.softcap_(logits, self.softcap) if self.softcap else logits

@@ -1,0 +1,77 @@
+"""A mixture of small gated feed-forward experts, of which every token uses the few with the largest router scores.
+
+Router: ``s = softmax(W_router h)`` over all experts, in 32-bit; the ``top`` largest scores are the chosen experts' weights
+as they are (no renormalising).  An expert: ``g = min(W_gate h, limit)``, ``u = clamp(W_up h, -limit, limit)``,
+``W_down (g * sigmoid(slope * g) * (u + 1))``, no biases.  An optional shared expert of the same form (sizes and limit of its
+own) runs for every token, weighted by ``sigmoid(W_sg h)``, one number a token.
+
+All experts' gate and up projections are one product, their down projections one product over the activations side by
+side; the kernel between the two multiplies each expert's activation by the token's weight for it, which is exactly zero
+for an expert that the token did not choose.  A token's result therefore does not depend on what else is in the batch.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import kernels
+from ..weights.loader import WeightDecl
+from .base import FeedForward
+from .linear import Linear
+from .registry import register_part
+
+
+@register_part("expert_mixture")
+class ExpertMixture(FeedForward):
+    """params: ``hidden_size``, ``experts``, ``top``, ``ff`` (an expert's inner size), ``limit``, ``shared_ff`` (0: no shared
+    expert), ``shared_limit``, ``slope`` (default 1.702), ``prefix``.  Tensors: ``router [experts, hidden]``,
+    ``e<i>.{gate,up} [ff, hidden]``, ``e<i>.down [hidden, ff]``, and with a shared expert ``shared.{gate,up,down}`` and
+    ``shared.sg [1, hidden]``."""
+
+    graph_safe = True
+
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        self.hidden, self.experts, self.top, self.ff = int(params["hidden_size"]), int(params["experts"]), int(params["top"]), int(params["ff"])
+        self.limit, self.slope = float(params["limit"]), float(params.get("slope", 1.702))
+        self.shared_ff, self.shared_limit = int(params.get("shared_ff") or 0), float(params.get("shared_limit") or 0.0)
+        if min(self.hidden, self.experts, self.top, self.ff) <= 0 or self.top > self.experts or self.shared_ff < 0:
+            raise ValueError(f"expert_mixture: {self.experts} experts of {self.ff}, top {self.top}, shared {self.shared_ff} are not served")
+        self.prefix = params.get("prefix", "")
+        self.cols = self.experts * self.ff + self.shared_ff
+        self.router = self.gate_up = self.down = None
+
+    def weight_decls(self):
+        p, W = self.prefix, self.hidden
+        decls = [WeightDecl(p + "router", (self.experts, W))]
+        for e in range(self.experts):
+            decls += [WeightDecl(f"{p}e{e}.gate", (self.ff, W)), WeightDecl(f"{p}e{e}.up", (self.ff, W)), WeightDecl(f"{p}e{e}.down", (W, self.ff))]
+        if self.shared_ff:
+            decls += [WeightDecl(p + "shared.gate", (self.shared_ff, W)), WeightDecl(p + "shared.up", (self.shared_ff, W)),
+                      WeightDecl(p + "shared.down", (W, self.shared_ff)), WeightDecl(p + "shared.sg", (1, W))]
+        return decls
+
+    def bind(self, tensors):
+        p = self.prefix
+        names = [f"e{e}." for e in range(self.experts)] + (["shared."] if self.shared_ff else [])
+        rows = [tensors[p + n + half] for n in names for half in ("gate", "up")]
+        downs = [tensors[p + n + "down"] for n in names]
+        if len({t.dtype for t in rows + downs}) > 1:
+            rows, downs = [t.float() for t in rows], [t.float() for t in downs]
+        self.gate_up = Linear(torch.cat(rows, dim=0).contiguous(), self.ctx.dtype)
+        self.down = Linear(torch.cat(downs, dim=1).contiguous(), self.ctx.dtype)
+        # the router (and the shared expert's gate behind it) in 32-bit
+        routes = [tensors[p + "router"].float()] + ([tensors[p + "shared.sg"].float()] if self.shared_ff else [])
+        self.router = Linear(torch.cat(routes, dim=0).contiguous(), self.ctx.dtype)
+
+    def modules(self):
+        return ["moe"] + self.router.modules() + self.gate_up.modules() + self.down.modules()
+
+    def linears(self):
+        return [self.router, self.gate_up, self.down]
+
+    def forward(self, x):
+        logits = self.router(x, out_dtype=torch.float32)
+        gu = self.gate_up(x)
+        y = torch.empty((x.shape[0], self.cols), dtype=self.ctx.dtype, device=x.device)
+        kernels.moe_activation(gu, logits, y, self.experts, self.top, self.ff, self.limit, self.shared_ff, self.shared_limit, self.slope)
+        return self.down(y, defer=self.defer_output)

@@ -67,14 +67,16 @@ class MLP(FeedForward):
 @register_part("gated_mlp")
 class GatedMLP(FeedForward):
     graph_safe = True
-    """params: ``hidden_size``, ``intermediate_size``, ``activation`` ("silu"), ``prefix``, ``names`` (the three tensors'
-    names after the prefix: ``gate``, ``up``, ``down``; default ``gate_proj.weight`` and so on)."""
+    """params: ``hidden_size``, ``intermediate_size``, ``activation`` (``silu``, or ``gelu_tanh``: the tanh form of gelu),
+    ``prefix``, ``names`` (the three tensors' names after the prefix: ``gate``, ``up``, ``down``; default ``gate_proj.weight``
+    and so on)."""
 
     def __init__(self, params, ctx):
         super().__init__(params, ctx)
         self.hidden, self.inter = int(params["hidden_size"]), int(params["intermediate_size"])
-        if params.get("activation", "silu") != "silu":
-            raise ValueError(f"gated_mlp: activation {params['activation']!r} is not implemented (only \"silu\")")
+        self.activation = params.get("activation", "silu")
+        if self.activation not in kernels._GATED_ACTIVATIONS:
+            raise ValueError(f"gated_mlp: activation {self.activation!r} is not implemented ({', '.join(kernels._GATED_ACTIVATIONS)})")
         self.prefix = params.get("prefix", "")
         self.names = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"}
         self.names.update(params.get("names") or {})
@@ -92,7 +94,7 @@ class GatedMLP(FeedForward):
         gate, up = tensors[p + n["gate"]], tensors[p + n["up"]]
         if gate.dtype != up.dtype:
             gate, up = gate.float(), up.float()
-        self.fused = (self.ctx.dtype == torch.bfloat16 and gate.dtype == torch.bfloat16
+        self.fused = (self.ctx.dtype == torch.bfloat16 and gate.dtype == torch.bfloat16 and self.activation == "silu"
                       and kernels.tensor_core_gemm_takes(2 * self.inter, self.hidden))
         if self.fused:
             # rows alternate gate_i, up_i: the tensor-core product applies SwiGLU in its epilogue
@@ -113,5 +115,8 @@ class GatedMLP(FeedForward):
             return self.down(self.gate_up(x, epilogue="swiglu"), defer=self.defer_output)
         gu = self.gate_up(x)
         z = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
-        kernels.swiglu(gu, z)
-        return self.down(z)
+        if self.activation == "silu":
+            kernels.swiglu(gu, z)
+        else:
+            kernels.gated_activation(gu, z, self.activation)
+        return self.down(z, defer=self.defer_output)

@@ -11,7 +11,7 @@ import torch
 
 from .. import kernels
 from ..weights.loader import WeightDecl
-from .base import Norm, ScaledParts
+from .base import Norm, NormedDelta, ScaledParts
 from .registry import register_part
 
 
@@ -98,3 +98,59 @@ class LayerNorm(Norm):
         (d1, s1), (d2, s2) = (terms + [(None, 1.0), (None, 1.0)])[:2]
         return kernels.layernorm(residual, self.weight, self.eps, out, delta=d1, delta_scale=scale * s1, delta2=d2, delta2_scale=scale * s2,
                                  rows=rows, write_back=bool(terms) and rows is None, center=self.center)
+
+
+@register_part("group_rms_norm")
+class GroupRMSNorm(Norm):
+    """RMS norm in groups: the row is cut into ``groups`` equal consecutive parts, each divided by its own
+    ``sqrt(mean(part^2) + eps)``, and the whole multiplied by a plain weight.  params: ``size``, ``groups``, ``eps``,
+    ``weight`` (the tensor's relative name).
+
+    It serves on both sides of a sublayer.  Ahead of one, ``forward_add(residual, delta)`` norms the stream; ``delta`` may
+    be a ``NormedDelta`` that a norm of this kind (same size, groups and eps) left behind a sublayer (``defer``), and the
+    one kernel then first adds ``scale * norm(y) * weight`` to the stream.  Behind one, ``defer(y, scale)`` makes that
+    record, and ``add_normed`` adds it at once."""
+
+    graph_safe = True
+    kernel_modules = ("group_norm",)
+
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        self.size, self.groups, self.eps = int(params["size"]), int(params.get("groups", 1)), float(params["eps"])
+        if self.groups <= 0 or self.size % self.groups:
+            raise ValueError(f"group_rms_norm: rows of {self.size} cannot be cut into {self.groups} equal groups")
+        self.weight_name = params.get("weight", "weight")
+        self.weight = None
+
+    def weight_decls(self):
+        return [WeightDecl(self.weight_name, (self.size,), init="one_plus_normal")]
+
+    def bind(self, tensors):
+        self.weight = tensors[self.weight_name].contiguous()
+
+    def defer(self, y, scale=1.0):
+        return NormedDelta(y, self.weight, float(scale))
+
+    def _pending(self, delta):
+        if delta is None:
+            return None, None, 1.0
+        if not isinstance(delta, NormedDelta):
+            raise ValueError("group_rms_norm: what is pending on the stream must be a sublayer output that a norm of this kind deferred")
+        return delta.y, delta.weight, delta.scale
+
+    def add_normed(self, residual, delta):
+        """``residual += scale * norm(y) * weight`` for a ``NormedDelta`` (32-bit, in place)."""
+        y, w, scale = self._pending(delta)
+        if y is not None:
+            kernels.group_norm(residual, self.groups, self.eps, y=y, y_weight=w, y_scale=scale)
+        return residual
+
+    def forward(self, x, out_dtype=None):
+        out = torch.empty(x.shape, dtype=out_dtype or self.ctx.dtype, device=x.device)
+        return kernels.group_norm(x, self.groups, self.eps, weight=self.weight, out=out)
+
+    def forward_add(self, residual, delta, rows=None, out_dtype=None):
+        y, w, scale = self._pending(delta)
+        n = residual.shape[0] if rows is None else rows.shape[0]
+        out = torch.empty((n, self.size), dtype=out_dtype or self.ctx.dtype, device=residual.device)
+        return kernels.group_norm(residual, self.groups, self.eps, y=y, y_weight=w, y_scale=scale, weight=self.weight, out=out, rows=rows)
