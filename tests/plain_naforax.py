@@ -34,8 +34,8 @@ def time_conv(h, kernel, bias=None):
 
 
 def sublayer_input(h, kernel):
-    """What a sublayer reads: its normed input plus that input's convolution over time."""
-    return h + time_conv(h, kernel)
+    """What a sublayer reads: its normed input plus that input's convolution over time (no kernel: the input itself)."""
+    return h if kernel is None else h + time_conv(h, kernel)
 
 
 def rotate_pairs(x, positions, base, dims):
@@ -78,7 +78,8 @@ def diff_attention(h, w, p, m, eps, probs=None):
     rep = H // G
     k, v = k.repeat_interleave(rep, dim=1), v.repeat_interleave(rep, dim=1)
     s = torch.einsum("ihmd,jhmd->mhij", q, k) * m["scale"]
-    s = s.masked_fill(~chunk_visible(T, m["mask"]["size"])[None, None], -math.inf)
+    size = m["mask"]["size"] if m.get("mask") is not None else T + 1          # no mask: every earlier key
+    s = s.masked_fill(~chunk_visible(T, size)[None, None], -math.inf)
     a = torch.softmax(s, dim=-1)
     if probs is not None:
         probs.append(a)
@@ -165,12 +166,12 @@ def run_order(cfg):
     return order + [(i, None, False) for i in range(loop["stop"], n)]
 
 
-def layer(x, w, cfg, i):
+def layer(x, w, cfg, i, probs=None, chosen=None):
     L, p = cfg["layers"][i], f"l{i}."
-    m, groups, eps = cfg["residual_mult"], cfg["norm"]["groups"], cfg["norm"]["eps"]
-    h = sublayer_input(group_norm(x, w[p + "norm1"], groups, eps), w[p + "canon1"])
+    m, groups, eps = cfg.get("residual_mult", 1.0), cfg["norm"].get("groups", 1), cfg["norm"]["eps"]
+    h = sublayer_input(group_norm(x, w[p + "norm1"], groups, eps), w.get(p + "canon1"))
     if L["type"] == "attention":
-        a = diff_attention(h, w, p + "mix.", L["mixer"], eps)
+        a = diff_attention(h, w, p + "mix.", L["mixer"], eps, probs)
     elif L["type"] == "mingru":
         a = mingru(h, w, p + "mix.")
     elif L["type"] == "mamba1":
@@ -180,14 +181,15 @@ def layer(x, w, cfg, i):
     x = x + m * group_norm(a, w[p + "norm1b"], groups, eps)
     mlp = L.get("mlp")
     if mlp is not None:
-        h = sublayer_input(group_norm(x, w[p + "norm2"], groups, eps), w[p + "canon2"])
-        f = dense_ff(h, w, p + "mlp.") if mlp["kind"] == "dense" else moe_ff(h, w, p + "mlp.", mlp)
+        h = sublayer_input(group_norm(x, w[p + "norm2"], groups, eps), w.get(p + "canon2"))
+        f = dense_ff(h, w, p + "mlp.") if mlp["kind"] == "dense" else moe_ff(h, w, p + "mlp.", mlp, chosen)
         x = x + m * group_norm(f, w[p + "norm2b"], groups, eps)
     return x
 
 
-def model(tokens, w, cfg, streams=None):
-    """Logits ``[T, vocab]`` of one whole sequence.  ``streams`` (a list) receives the residual stream after every layer run."""
+def model(tokens, w, cfg, streams=None, probs=None, chosen=None):
+    """Logits ``[T, vocab]`` of one whole sequence.  ``streams`` (a list) receives the residual stream after every layer run,
+    ``probs`` the attention maps of every attention layer run, ``chosen`` the experts that every mixture layer run chose."""
     w = {k: v.to(F) for k, v in w.items()}
     first = w["embed"][torch.as_tensor(tokens, dtype=torch.long)]
     x = first
@@ -196,10 +198,87 @@ def model(tokens, w, cfg, streams=None):
             if t > 0:
                 x = x + first
             x = x + w["loop.step"][t]
-        x = layer(x, w, cfg, i)
+        x = layer(x, w, cfg, i, probs, chosen)
         if streams is not None:
             streams.append(x)
-    x = group_norm(x, w["final.norm"], cfg["norm"]["groups"], cfg["norm"]["eps"])
+    x = group_norm(x, w["final.norm"], cfg["norm"].get("groups", 1), cfg["norm"]["eps"])
     logits = x @ w["head"].T
     cap = cfg.get("logit_softcap")
     return cap * torch.tanh(logits / cap) if cap else logits
+
+
+def forward(w, cfg, tokens, **more):
+    return model(tokens, w, cfg, **more)
+
+
+def tensor_shapes(cfg):
+    """name -> shape of every tensor a checkpoint of this configuration holds."""
+    W, out = cfg["width"], {}
+    out["embed"], out["head"], out["final.norm"] = (cfg["vocab"], W), (cfg["vocab"], W), (W,)
+    loop = cfg.get("loop")
+    if loop and loop["start"] < loop["stop"]:
+        out["loop.step"] = (loop["times"], W)
+    taps = (cfg.get("canon") or {}).get("taps", 0)
+    for i, L in enumerate(cfg["layers"]):
+        p, m, mlp = f"l{i}.", L["mixer"], L.get("mlp")
+        out[p + "norm1"], out[p + "norm1b"] = (W,), (W,)
+        if taps:
+            out[p + "canon1"] = (W, taps)
+        if L["type"] == "attention":
+            H, G, d, vd = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            out.update({p + "mix.q": (2 * H * d, W), p + "mix.q.b": (2 * H * d,), p + "mix.k": (2 * G * d, W), p + "mix.k.b": (2 * G * d,),
+                        p + "mix.v": (G * vd, W), p + "mix.v.b": (G * vd,), p + "mix.q.norm": (d,), p + "mix.k.norm": (d,),
+                        p + "mix.g": (H * vd, W), p + "mix.o": (W, H * vd), p + "mix.o.b": (W,)})
+            out.update({p + "mix." + n: (d,) for n in ("lq1", "lk1", "lq2", "lk2")})
+        elif L["type"] == "mingru":
+            n = m["width"]
+            out.update({p + "mix.z": (n, W), p + "mix.z.b": (n,), p + "mix.x": (n, W), p + "mix.x.b": (n,), p + "mix.g": (n, W), p + "mix.o": (W, n)})
+        else:
+            I, N, R = m["inner"], m["state"], m["dt_rank"]
+            out.update({p + "mix.in": (2 * I, W), p + "mix.conv": (I, m["conv"]), p + "mix.conv.b": (I,), p + "mix.x": (R + 2 * N, I),
+                        p + "mix.dt": (I, R), p + "mix.dt.b": (I,), p + "mix.A_log": (I, N), p + "mix.D": (I,), p + "mix.o": (W, I)})
+        if mlp is None:
+            continue
+        out[p + "norm2"], out[p + "norm2b"] = (W,), (W,)
+        if taps:
+            out[p + "canon2"] = (W, taps)
+        if mlp["kind"] == "dense":
+            out.update({p + "mlp.gate": (mlp["ff"], W), p + "mlp.up": (mlp["ff"], W), p + "mlp.down": (W, mlp["ff"])})
+        else:
+            names = [(f"e{e}.", mlp["expert"]["ff"]) for e in range(mlp["router"]["experts"])]
+            if mlp.get("shared") is not None:
+                names.append(("shared.", mlp["shared"]["ff"]))
+                out[p + "mlp.shared.sg"] = (1, W)
+            out[p + "mlp.router"] = (mlp["router"]["experts"], W)
+            for n, ff in names:
+                out.update({p + "mlp." + n + "gate": (ff, W), p + "mlp." + n + "up": (ff, W), p + "mlp." + n + "down": (W, ff)})
+    return out
+
+
+def random_weights(cfg, seed, gain=1.0):
+    """Seeded bfloat16 tensors: matrices ``N(0, gain^2 / in)``, gains of norms near one, small biases, decays and step sizes
+    of the scan in a range where the state neither dies at once nor keeps everything, a router whose scores differ."""
+    g = torch.Generator().manual_seed(seed)
+    out = {}
+    for name, shape in tensor_shapes(cfg).items():
+        last = name.split(".")[-1]
+        if name.endswith("A_log"):
+            t = torch.log(1.0 + torch.arange(shape[1], dtype=torch.float32) * 0.5)[None, :] + 0.2 * torch.randn(shape, generator=g) - 1.0
+        elif name.endswith("dt.b"):
+            t = torch.randn(shape, generator=g) * 0.5 - 1.0
+        elif last in ("norm1", "norm1b", "norm2", "norm2b") or name in ("final.norm",) or name.endswith(".D") or name.endswith("q.norm") or name.endswith("k.norm"):
+            t = 1.0 + 0.2 * torch.randn(shape, generator=g)
+        elif last in ("lq1", "lk1", "lq2", "lk2"):
+            t = 0.3 * torch.randn(shape, generator=g)
+        elif last == "b":
+            t = 0.3 * torch.randn(shape, generator=g)
+        elif last in ("canon1", "canon2", "conv"):
+            t = 0.5 * torch.randn(shape, generator=g)
+        elif name in ("embed", "loop.step"):
+            t = torch.randn(shape, generator=g)
+        elif last == "router" or last == "sg":
+            t = 3.0 * torch.randn(shape, generator=g) / math.sqrt(shape[-1])
+        else:
+            t = gain * torch.randn(shape, generator=g) / math.sqrt(shape[-1])
+        out[name] = t.to(torch.bfloat16)
+    return out
