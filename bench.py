@@ -3,7 +3,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--shape 8b|14b|32b] [--batch B] [--context C] [--impl ours|reference]
     python bench.py --workload mixed [--shape 14b] [--requests 64] [--budget 2048]     (a continuous batch through LLMEngine; its own line)
-    python bench.py --workload nezolorn | daronex [--layers 6] [--prefill-tokens 2048]   (another design beside Qwen3 at equal layer sizes; its own line)
+    python bench.py --workload nezolorn | daronex | naforax [--layers 6] [--prefill-tokens 2048]   (another design beside Qwen3 at equal layer sizes; its own line)
 
 The model has the layer sizes of Qwen3-8B (36 layers, hidden 4096, 32 query heads, 8 key/value
 heads, head size 128, intermediate 12288, vocabulary 151936, untied head) with seeded random
@@ -625,6 +625,84 @@ def daronex_workload(args) -> int:
     return 0
 
 
+def naforax_workload(args) -> int:
+    """``--workload naforax``: prefill and decode throughput of the Naforax design (layers of differential attention over
+    chunks, of the minimal gated recurrent unit and of the selective scan, a norm on both sides of every sublayer, input
+    convolutions, dense and expert-mixture feed-forwards) at two layer sizes that resemble real models, beside the engine's
+    Qwen3 model with the same width, query heads, feed-forward size, vocabulary and number of layers, all with seeded random
+    weights in bfloat16.  Measured as ``--workload nezolorn`` is: one prompt of ``--prefill-tokens`` tokens, decoding at
+    batch 8 and 64 from ``--context`` tokens through the decode graphs, and each kernel's time inside one prompt step and
+    one decode step of batch 64."""
+    hbm_gbs, bf16_tflops, _, peak_src = peaks()
+    layers, vocab, page = args.layers or 6, 32000, 16
+    T, ctx = args.prefill_tokens, min(args.context, 4096)
+    chunk = 1536                   # a decoded token at 4,096 sees 1,025 keys; the prompt crosses one chunk edge
+    # two maps of `dim` side by side fill the 128-wide cache row that the tensor-core attention kernels take
+    sizes = {"width2048": dict(width=2048, heads=16, kv=4, hd=128, ff=8192, dim=64, vdim=128, gru=4096, inner=4096, state=16, dt_rank=128,
+                               experts=8, top=2, expert_ff=2048, shared_ff=4096),
+             "width4096": dict(width=4096, heads=16, kv=4, hd=128, ff=12288, dim=64, vdim=128, gru=8192, inner=8192, state=16, dt_rank=256,
+                               experts=8, top=2, expert_ff=3072, shared_ff=6144)}
+
+    def configs(z):
+        dense = {"kind": "dense", "ff": z["ff"]}
+        moe = {"kind": "moe", "router": {"experts": z["experts"], "top": z["top"]}, "expert": {"ff": z["expert_ff"], "limit": 7.0},
+               "shared": {"ff": z["shared_ff"], "limit": 7.0}}
+        attn = {"type": "attention", "mlp": dense,
+                "mixer": {"heads": z["heads"], "kv_heads": z["kv"], "dim": z["dim"], "vdim": z["vdim"], "diff": 0.5, "scale": z["dim"] ** -0.5,
+                          "mask": {"size": chunk}, "rot": {"base": 500000.0, "dims": 32}}}
+        gru = {"type": "mingru", "mlp": moe, "mixer": {"width": z["gru"]}}
+        scan = {"type": "mamba1", "mlp": moe, "mixer": {"inner": z["inner"], "state": z["state"], "dt_rank": z["dt_rank"], "conv": 4}}
+        nx = {"architecture": "Naforax", "vocab": vocab, "width": z["width"], "norm": {"eps": 1e-6, "groups": 2}, "canon": {"taps": 3},
+              "residual_mult": 0.5, "logit_softcap": 30.0, "loop": None, "layers": [(attn, gru, scan)[i % 3] for i in range(layers)]}
+        qw = dict(QWEN3_8B)
+        qw.update({"num_hidden_layers": layers, "hidden_size": z["width"], "num_attention_heads": z["heads"], "num_key_value_heads": z["kv"],
+                   "head_dim": z["hd"], "intermediate_size": z["ff"], "vocab_size": vocab})
+        return {"naforax": nx, "qwen3": qw}
+
+    def measure(cfg_json, z, name):
+        def annotate(res, rate):
+            W, H = z["width"], z["heads"]
+            if name == "naforax":
+                n_att, n_gru, n_scan = (sum(1 for i in range(layers) if i % 3 == k) for k in range(3))
+                n_moe = n_gru + n_scan
+                keys = sum(p % chunk + 1 for p in range(T))
+                # as the kernel runs it: two maps a head as query heads over rows of 128 (scores and values)
+                rate("kernels_prefill", "attention_tc.spy_attention_tc", flops=4.0 * keys * 2 * H * z["hd"] * n_att)
+                rate("kernels_decode_b64", "attention_decode.spy_attention_decode", nbytes=64.0 * z["kv"] * (ctx % chunk + 1) * z["hd"] * 2 * 2 * n_att)
+                # both norms of a sublayer in one launch: reads the sublayer's 32-bit output and the stream, writes the stream and the normed row
+                for block, rows in (("kernels_prefill", T), ("kernels_decode_b64", 64)):
+                    rate(block, "group_norm.spy_group_norm", nbytes=float(2 * layers) * rows * W * (4 + 4 + 4 + 2))
+                    rate(block, "time_conv.spy_time_conv", nbytes=float(2 * layers) * rows * W * 4 + float(n_scan) * rows * z["inner"] * 6)
+                    cols = z["experts"] * z["expert_ff"] + z["shared_ff"]
+                    rate(block, "moe.spy_moe_activation", nbytes=float(n_moe) * rows * cols * 6)
+                    rate(block, "gated_scan.spy_mingru_scan", nbytes=float(n_gru) * (rows * z["gru"] * (12 + 2) + (64 * z["gru"] * 8 if rows == 64 else 0)))
+                    rate(block, "gated_scan.spy_selective_scan",
+                         nbytes=float(n_scan) * (rows * z["inner"] * (2 + 4 + 4 + 2) + (64 * z["inner"] * z["state"] * 8 if rows == 64 else 0)))
+            else:
+                rate("kernels_prefill", "attention_tc.spy_attention_tc", flops=4.0 * (T * (T + 1) / 2) * H * z["hd"] * layers)
+                rate("kernels_decode_b64", "attention_decode.spy_attention_decode", nbytes=64.0 * z["kv"] * (ctx + 1) * z["hd"] * 2 * 2 * layers)
+                for block, rows in (("kernels_prefill", T), ("kernels_decode_b64", 64)):
+                    rate(block, "rmsnorm.spy_rmsnorm", nbytes=float(2 * layers) * rows * W * (4 + 4 + 4 + 2))
+                    rate(block, "swiglu.spy_swiglu", nbytes=float(layers) * rows * z["ff"] * 6)
+
+        return _measure_design(args, cfg_json, vocab, page, T, ctx, annotate)
+
+    out_sizes = {}
+    with ClockSampler() as clocks:
+        for tag, z in sizes.items():
+            out_sizes[tag] = {"layer_sizes": z, "layers": layers}
+            for name, cfg_json in configs(z).items():
+                out_sizes[tag][name] = measure(cfg_json, z, name)
+    print(json.dumps({"metric": "prefill and decode tokens/s of the Naforax design beside Qwen3 at equal layer sizes (bf16, random weights)",
+                      "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": 3, "dtype": "bf16",
+                      "data": "synthetic: seeded random weights and random token ids",
+                      "config": {"layers": layers, "vocab": vocab, "prefill_tokens": T, "decode_context": ctx, "chunk": chunk, "page_size": page,
+                                 "pattern": "differential attention with a dense feed-forward, minGRU with an expert mixture, selective scan with an expert mixture; repeated",
+                                 "timing": "CUDA events; inputs (weights, caches and states of 64 requests) exceed L2"},
+                      "peaks": {"hbm_gbs": hbm_gbs, "bf16_tflops": bf16_tflops, "source": peak_src}, "sizes": out_sizes, "clocks": clocks.summary()}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -639,9 +717,9 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1/64 and short-context points")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel rooflines")
-    ap.add_argument("--workload", default="decode", choices=["decode", "mixed", "nezolorn", "daronex"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "mixed", "nezolorn", "daronex", "naforax"],
                     help="decode: the contract's line (default); mixed: a continuous batch of --requests requests with prompts of 64 to 2,048 "
-                         "tokens and 128 generated tokens each through LLMEngine, its own line; nezolorn, daronex: prefill and decode of that design "
+                         "tokens and 128 generated tokens each through LLMEngine, its own line; nezolorn, daronex, naforax: prefill and decode of that design "
                          "beside Qwen3 at equal layer sizes, its own line")
     ap.add_argument("--requests", type=int, default=64, help="mixed workload: number of requests")
     ap.add_argument("--budget", type=int, default=2048, help="mixed workload: max_num_batched_tokens")
@@ -662,6 +740,8 @@ def main() -> int:
         return nezolorn_workload(args)
     if args.workload == "daronex":
         return daronex_workload(args)
+    if args.workload == "naforax":
+        return naforax_workload(args)
     hbm_gbs, bf16_tflops, bf16_sustained, peak_src = peaks()
     cfg_json = dict(QWEN3_8B)
     cfg_json.update(SHAPES[args.shape])
