@@ -67,12 +67,58 @@ gemm_simt_kernel(const TA* __restrict__ A, long long lda, const TW* __restrict__
 }
 
 // Row strides lda/ldw/ldc are in elements.
+
+// A product with few output columns (a router, a gate of one number a token): a warp owns one row of A and up to SKINNY_NG
+// columns at a time; its lanes stride over k, so every load is a run of 32 consecutive elements, and the lanes' sums are
+// added in a fixed order.  A row's result does not depend on M either.
+constexpr int SKINNY_N = 32, SKINNY_NG = 8;
+
+template <typename TA, typename TW, typename TC>
+__global__ void __launch_bounds__(128)
+gemm_skinny_kernel(const TA* __restrict__ A, long long lda, const TW* __restrict__ W, long long ldw, TC* __restrict__ C, long long ldc,
+                   int M, int N, int K)
+{
+    pdl_enter();
+    const int lane = threadIdx.x & 31;
+    const long long m = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (m >= M) return;
+    const TA* a = A + m * lda;
+    for (int n0 = 0; n0 < N; n0 += SKINNY_NG) {
+        float acc[SKINNY_NG];
+#pragma unroll
+        for (int j = 0; j < SKINNY_NG; ++j) acc[j] = 0.f;
+        for (int k = lane; k < K; k += 32) {
+            const float av = to_f32(a[k]);
+#pragma unroll
+            for (int j = 0; j < SKINNY_NG; ++j)
+                if (n0 + j < N) acc[j] = fmaf(av, to_f32(W[(size_t)(n0 + j) * ldw + k]), acc[j]);
+        }
+#pragma unroll
+        for (int j = 0; j < SKINNY_NG; ++j) {
+            const float sum = warp_sum(acc[j]);
+            if (lane == 0 && n0 + j < N) C[m * ldc + n0 + j] = from_f32<TC>(sum);
+        }
+    }
+}
+
 extern "C" int spy_gemm_simt(const void* A, int a_dtype, long long lda, const void* W, int w_dtype, long long ldw, void* C, int c_dtype,
                              long long ldc, int M, int N, int K, cudaStream_t stream)
 {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0) SPY_FAIL("gemm: K %d must be positive", K);
     if (lda < K || ldw < K || ldc < N) SPY_FAIL("gemm: row strides %lld/%lld/%lld are shorter than the rows", lda, ldw, ldc);
+    if (N <= SKINNY_N) {                                      // chosen by the weight's shape alone, as every choice of a product is
+        SPY_DISPATCH_DTYPE(a_dtype, TA, {
+            SPY_DISPATCH_DTYPE(w_dtype, TW, {
+                SPY_DISPATCH_DTYPE(c_dtype, TC, {
+                    spy_launch(gemm_skinny_kernel<TA, TW, TC>, dim3((unsigned)(((long long)M + 3) / 4)), dim3(128), 0, stream, (const TA*)A, lda,
+                               (const TW*)W, ldw, (TC*)C, ldc, M, N, K);
+                })
+            })
+        })
+        SPY_CHECK_LAUNCH("gemm_skinny");
+        return 0;
+    }
     const long long gy = ((long long)M + BM - 1) / BM;
     if (gy > 65535) SPY_FAIL("gemm: M %d exceeds the grid limit of this kernel (%d rows)", M, 65535 * BM);
     dim3 grid((N + BN - 1) / BN, (unsigned)gy);

@@ -1130,10 +1130,11 @@ def diff_combine(attn: torch.Tensor, hd: int, gate: Optional[torch.Tensor], gate
 
 
 def mingru_scan(proj: torch.Tensor, z_col: int, x_col: int, g_col: int, z_bias: Optional[torch.Tensor], x_bias: Optional[torch.Tensor], state: torch.Tensor,
-                q_start: torch.Tensor, state_slot: torch.Tensor, num_seqs: int, out: torch.Tensor, width: int) -> torch.Tensor:
+                q_start: torch.Tensor, state_slot: torch.Tensor, num_seqs: int, out: torch.Tensor, width: int, longest: Optional[int] = None) -> torch.Tensor:
     """``S <- (1 - z) S + z c`` element by element over every request's tokens of this step, from and into ``state [slots, width]``;
     ``z = sigmoid(proj[:, z_col..] + z_bias)``, ``u = proj[:, x_col..] + x_bias``, ``c = u + 1/2`` where ``u >= 0`` else
-    ``sigmoid(u)``; ``out = S * silu(proj[:, g_col..])``.  ``proj`` float32."""
+    ``sigmoid(u)``; ``out = S * silu(proj[:, g_col..])``.  ``proj`` float32.  ``longest``: no request brings more tokens than this
+    (default: the step's token count); long runs are scanned in slices that run side by side."""
     _check(proj, "fused projection", torch.float32, 2)
     _check(state, "recurrent state", torch.float32, 2)
     _check(out, "recurrence output", ndim=2)
@@ -1148,19 +1149,20 @@ def mingru_scan(proj: torch.Tensor, z_col: int, x_col: int, g_col: int, z_bias: 
                 raise KernelError("mingru_scan: the biases have one entry per channel and one dtype")
     some = z_bias if z_bias is not None else x_bias
     _call("gated_scan", "spy_mingru_scan", _ptr(proj), ctypes.c_longlong(proj.shape[1]), int(z_col), int(x_col), int(g_col), _ptr(z_bias), _ptr(x_bias),
-          _code(some, "gate bias") if some is not None else 0, _ptr(state), _ptr(q_start), _ptr(state_slot), int(num_seqs), _ptr(out),
+          _code(some, "gate bias") if some is not None else 0, _ptr(state), _ptr(q_start), _ptr(state_slot), int(num_seqs),
+          int(longest if longest is not None else proj.shape[0]), _ptr(out),
           _code(out, "recurrence output"), int(width), _stream())
     return out
 
 
 def selective_scan(x: torch.Tensor, dt_pre: torch.Tensor, dt_bias: torch.Tensor, proj: torch.Tensor, b_col: int, c_col: int, z: torch.Tensor, z_col: int,
                    a_log: torch.Tensor, d_skip: torch.Tensor, state: torch.Tensor, q_start: torch.Tensor, state_slot: torch.Tensor, num_seqs: int,
-                   out: torch.Tensor) -> torch.Tensor:
+                   out: torch.Tensor, longest: Optional[int] = None) -> torch.Tensor:
     """The selective scan over every request's tokens of this step, from and into ``state [slots, inner * n]``:
     ``dt = softplus(dt_pre + dt_bias)``, ``S[c, n] <- exp(-dt_c exp(a_log[c, n])) S[c, n] + dt_c x_c B_n``,
     ``y_c = sum_n S[c, n] C_n + d_skip_c x_c``, ``out = y * silu(z)``.  ``x [T, inner]``; ``dt_pre [T, inner]`` float32;
     ``proj`` float32 holds ``B`` and ``C`` (``n`` columns each) at ``b_col`` and ``c_col``; ``z`` float32 holds the gate's
-    ``inner`` columns from ``z_col``."""
+    ``inner`` columns from ``z_col``.  ``longest`` as for ``mingru_scan``."""
     _check(x, "scan input", ndim=2)
     T, inner = x.shape
     _check(dt_pre, "step size pre-activation", torch.float32, 2)
@@ -1178,7 +1180,7 @@ def selective_scan(x: torch.Tensor, dt_pre: torch.Tensor, dt_bias: torch.Tensor,
     z_view_ptr = ctypes.c_void_p(z.data_ptr() + 4 * z_col)
     _call("gated_scan", "spy_selective_scan", _ptr(x), _code(x, "scan input"), _ptr(dt_pre), _ptr(dt_bias), _ptr(proj), ctypes.c_longlong(proj.shape[1]),
           int(b_col), int(c_col), z_view_ptr, ctypes.c_longlong(z.shape[1]), _ptr(a_log), _ptr(d_skip), _code(a_log, "A_log"), _ptr(state), _ptr(q_start),
-          _ptr(state_slot), int(num_seqs), _ptr(out), _code(out, "scan output"), inner, n, _stream())
+          _ptr(state_slot), int(num_seqs), int(longest if longest is not None else T), _ptr(out), _code(out, "scan output"), inner, n, _stream())
     return out
 
 

@@ -69,7 +69,8 @@ class MinGRU(Mixer):
         n = self.width
         proj = self.fused(x, out_dtype=torch.float32)
         y = torch.empty((x.shape[0], n), dtype=self.ctx.dtype, device=x.device)
-        kernels.mingru_scan(proj, 0, n, 2 * n, self.bias_z, self.bias_x, cache.state, batch.q_start, batch.state_slot, batch.num_seqs, y, n)
+        kernels.mingru_scan(proj, 0, n, 2 * n, self.bias_z, self.bias_x, cache.state, batch.q_start, batch.state_slot, batch.num_seqs, y, n,
+                            longest=1 if batch.one_token_each else batch.num_tokens)
         return self.o(y, defer=self.defer_output, out_dtype=self.output_dtype)
 
 
@@ -130,5 +131,5 @@ class SelectiveScan(Mixer):
         dt_pre = self.w_dt(low, out_dtype=torch.float32)
         y = torch.empty((T, I), dtype=self.ctx.dtype, device=x.device)
         kernels.selective_scan(xc, dt_pre, self.dt_bias, proj, R, R + N, xz, I, self.a_log, self.d_skip, scan_state.state, batch.q_start, batch.state_slot,
-                               batch.num_seqs, y)
+                               batch.num_seqs, y, longest=1 if batch.one_token_each else batch.num_tokens)
         return self.o(y, defer=self.defer_output, out_dtype=self.output_dtype)

@@ -305,6 +305,12 @@ def test_group_norm_adds_a_normed_output_and_norms_the_stream_for_the_next_subla
         kernels.group_norm(torch.zeros(2, 10, device="cuda"), 3, 1e-5, weight=torch.ones(10, device="cuda"), out=torch.empty(2, 10, device="cuda"))
 
 
+# two requests' lengths and how they are cut into five steps: runs that stay short, and runs that are long in some steps (one of
+# 100 tokens beside one of 4, then one token each, then 46 beside 11) with single tokens and pairs in between
+RUNS = {"short": ({0: 20, 1: 9}, {0: [2, 1, 9, 1, 7], 1: [1, 2, 4, 1, 1]}),
+        "long": ({0: 150, 1: 37}, {0: [2, 1, 100, 1, 46], 1: [1, 20, 4, 1, 11]})}
+
+
 def _two_requests_in_portions(lens, cuts, feed):
     """Runs ``feed(parts, q_start, slots, one_each)`` for every step of two requests (in slots 0 and 2 of three) cut into
     portions; ``parts`` is [(request, first token, count)]."""
@@ -356,12 +362,14 @@ def test_convolution_over_time_keeps_its_last_inputs_through_portions_and_slots(
 
 
 @gpu
+@pytest.mark.parametrize("runs", ["short", "long"])
 @pytest.mark.parametrize("width,extra", [(24, 0), (80, 5), (320, 0), (1, 2)])
-def test_mingru_scan_carries_its_state_through_portions_and_slots(width, extra):
+def test_mingru_scan_carries_its_state_through_portions_and_slots(width, extra, runs):
+    """Short runs take the kernel that walks a run in order, long ones the kernel that scans slices of a run side by side."""
     from spyinfer_b200 import kernels
 
     g = torch.Generator().manual_seed(width)
-    lens, cuts = {0: 20, 1: 9}, {0: [2, 1, 9, 1, 7], 1: [1, 2, 4, 1, 1]}
+    lens, cuts = RUNS[runs]
     ld = 3 * width + extra
     cols = (extra, extra + 2 * width, extra + width)              # z, the candidate, the output gate: in no particular order
     proj = {s: torch.randn(t, ld, generator=g) * 2 for s, t in lens.items()}
@@ -394,12 +402,13 @@ def test_mingru_scan_carries_its_state_through_portions_and_slots(width, extra):
 
 
 @gpu
+@pytest.mark.parametrize("runs", ["short", "long"])
 @pytest.mark.parametrize("inner,n,rank", [(24, 5, 2), (72, 8, 6), (48, 16, 3), (256, 64, 8), (40, 33, 4), (8, 1, 1)])
-def test_selective_scan_carries_its_states_through_portions_and_slots(inner, n, rank):
+def test_selective_scan_carries_its_states_through_portions_and_slots(inner, n, rank, runs):
     from spyinfer_b200 import kernels
 
     g = torch.Generator().manual_seed(inner + n)
-    lens, cuts = {0: 20, 1: 9}, {0: [2, 1, 9, 1, 7], 1: [1, 2, 4, 1, 1]}
+    lens, cuts = RUNS[runs]
     x = {s: torch.randn(t, inner, generator=g) for s, t in lens.items()}
     dt_pre = {s: torch.randn(t, inner, generator=g) * 2 for s, t in lens.items()}
     proj = {s: torch.randn(t, rank + 2 * n, generator=g) for s, t in lens.items()}
