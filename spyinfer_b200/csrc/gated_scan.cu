@@ -122,7 +122,29 @@ extern "C" int spy_mingru_scan(const float* proj, long long ld, int z_col, int x
     return 0;
 }
 
-constexpr int SS_PER_THREAD = 16;      // states a thread keeps in registers; a channel's states are dealt out over `lanes` threads
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr int SS_PER_THREAD = 16;
+// 2^v by the special-function unit (two units in the last place at most): the decays of the selective scan, of which a long
+// run needs one for every token, channel and state, twice
+__device__ __forceinline__ float fast_exp2(float v)
+{
+    float r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v));
+    return r;
+}
+
+// four consecutive entries of a token's B or C row, as one 16-byte load where the row allows it
+__device__ __forceinline__ float4 row_quad(const float* __restrict__ p, int n, int n_state, bool vec)
+{
+    if (vec) return __ldg(reinterpret_cast<const float4*>(p + n));
+    float4 v;
+    v.x = n < n_state ? __ldg(p + n) : 0.f;
+    v.y = n + 1 < n_state ? __ldg(p + n + 1) : 0.f;
+    v.z = n + 2 < n_state ? __ldg(p + n + 2) : 0.f;
+    v.w = n + 3 < n_state ? __ldg(p + n + 3) : 0.f;
+    return v;
+}
+      // states a thread keeps in registers; a channel's states are dealt out over `lanes` threads
 
 template <typename TX, typename TW, typename TO>
 __global__ void selective_scan_kernel(const TX* __restrict__ x, const float* __restrict__ dt_pre, const TW* __restrict__ dt_bias,
@@ -136,6 +158,7 @@ __global__ void selective_scan_kernel(const TX* __restrict__ x, const float* __r
     const int c = idx / lanes, part = idx % lanes, seq = blockIdx.y;
     const int start = q_start[seq], end = q_start[seq + 1];
     const bool live = c < inner && start < end;          // threads past the last channel still take part in the shuffles
+    const bool quads = lanes == 1 && n_state % 4 == 0 && ((proj_ld | b_col | c_col) & 3) == 0;      // B and C rows by 16-byte loads
     const int cc = live ? c : 0;
     float A[SS_PER_THREAD], S[SS_PER_THREAD];
     float* st = state + ((long long)state_slot[seq] * inner + cc) * n_state;
@@ -143,8 +166,16 @@ __global__ void selective_scan_kernel(const TX* __restrict__ x, const float* __r
     for (int j = 0; j < SS_PER_THREAD; ++j) {
         const int n = part + j * lanes;
         const bool ok = live && n < n_state;
-        A[j] = ok ? -expf(to_f32(a_log[(long long)cc * n_state + n])) : 0.f;
-        S[j] = ok ? st[n] : 0.f;
+        A[j] = ok ? -expf(to_f32(a_log[(long long)cc * n_state + n])) * LOG2E : 0.f;        // decays as powers of two
+        S[j] = ok && !quads ? st[n] : 0.f;
+    }
+    if (quads && live) {                                     // the thread's states are a run of whole quads
+#pragma unroll
+        for (int j = 0; j < SS_PER_THREAD; j += 4) {
+            if (j >= n_state) break;
+            const float4 v = *reinterpret_cast<const float4*>(st + j);
+            S[j] = v.x; S[j + 1] = v.y; S[j + 2] = v.z; S[j + 3] = v.w;
+        }
     }
     const float bias = live ? to_f32(dt_bias[cc]) : 0.f, D = live ? to_f32(d_skip[cc]) : 0.f;
     for (int t = start; t < end; ++t) {
@@ -155,12 +186,25 @@ __global__ void selective_scan_kernel(const TX* __restrict__ x, const float* __r
         const float* B = proj + (long long)t * proj_ld + b_col;
         const float* C = proj + (long long)t * proj_ld + c_col;
         float y = 0.f;
+        if (lanes == 1) {
 #pragma unroll
-        for (int j = 0; j < SS_PER_THREAD; ++j) {
-            const int n = part + j * lanes;
-            if (n < n_state) {
-                S[j] = expf(dt * A[j]) * S[j] + dx * __ldg(B + n);
-                y = fmaf(S[j], __ldg(C + n), y);
+            for (int j = 0; j < SS_PER_THREAD; j += 4) {
+                if (j >= n_state) break;
+                const float4 b = row_quad(B, j, n_state, quads), cq = row_quad(C, j, n_state, quads);
+                S[j] = fast_exp2(dt * A[j]) * S[j] + dx * b.x;
+                S[j + 1] = fast_exp2(dt * A[j + 1]) * S[j + 1] + dx * b.y;
+                S[j + 2] = fast_exp2(dt * A[j + 2]) * S[j + 2] + dx * b.z;
+                S[j + 3] = fast_exp2(dt * A[j + 3]) * S[j + 3] + dx * b.w;
+                y = fmaf(S[j], cq.x, fmaf(S[j + 1], cq.y, fmaf(S[j + 2], cq.z, fmaf(S[j + 3], cq.w, y))));
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < SS_PER_THREAD; ++j) {
+                const int n = part + j * lanes;
+                if (n < n_state) {
+                    S[j] = fast_exp2(dt * A[j]) * S[j] + dx * __ldg(B + n);
+                    y = fmaf(S[j], __ldg(C + n), y);
+                }
             }
         }
         for (int o = lanes >> 1; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
@@ -170,7 +214,13 @@ __global__ void selective_scan_kernel(const TX* __restrict__ x, const float* __r
             out[(long long)t * inner + cc] = from_f32<TO>(y * (zv * sigmoidf_(zv)));
         }
     }
-    if (live) {
+    if (live && quads) {
+#pragma unroll
+        for (int j = 0; j < SS_PER_THREAD; j += 4) {
+            if (j >= n_state) break;
+            *reinterpret_cast<float4*>(st + j) = make_float4(S[j], S[j + 1], S[j + 2], S[j + 3]);
+        }
+    } else if (live) {
 #pragma unroll
         for (int j = 0; j < SS_PER_THREAD; ++j) {
             const int n = part + j * lanes;
@@ -202,13 +252,14 @@ selective_scan_sliced_kernel(const TX* __restrict__ x, const float* __restrict__
     const int per = (L + TS - 1) / TS;
     const int t0 = start + min(ts * per, L), t1 = start + min((ts + 1) * per, L);
     const bool live = c < inner;
+    const bool quads = lanes == 1 && n_state % 4 == 0 && ((proj_ld | b_col | c_col) & 3) == 0;      // B and C rows by 16-byte loads
     const int cc = live ? c : 0;
     float A[SS_PER_THREAD], S[SS_PER_THREAD];
     float* st = state + ((long long)state_slot[seq] * inner + cc) * n_state;
 #pragma unroll
     for (int j = 0; j < SS_PER_THREAD; ++j) {
         const int n = part + j * lanes;
-        A[j] = (live && n < n_state) ? -expf(to_f32(a_log[(long long)cc * n_state + n])) : 0.f;
+        A[j] = (live && n < n_state) ? -expf(to_f32(a_log[(long long)cc * n_state + n])) * LOG2E : 0.f;       // decays as powers of two
         S[j] = 0.f;
     }
     const float bias = live ? to_f32(dt_bias[cc]) : 0.f, D = live ? to_f32(d_skip[cc]) : 0.f;
@@ -219,10 +270,22 @@ selective_scan_sliced_kernel(const TX* __restrict__ x, const float* __restrict__
         const float dx = dt * (live ? to_f32(x[(long long)t * inner + cc]) : 0.f);
         const float* B = proj + (long long)t * proj_ld + b_col;
         sum_dt += dt;
+        if (lanes == 1) {                                        // the thread's states are a run: B by quads
 #pragma unroll
-        for (int j = 0; j < SS_PER_THREAD; ++j) {
-            const int n = part + j * lanes;
-            if (n < n_state) S[j] = expf(dt * A[j]) * S[j] + dx * __ldg(B + n);
+            for (int j = 0; j < SS_PER_THREAD; j += 4) {
+                if (j >= n_state) break;
+                const float4 b = row_quad(B, j, n_state, quads);
+                S[j] = fast_exp2(dt * A[j]) * S[j] + dx * b.x;
+                S[j + 1] = fast_exp2(dt * A[j + 1]) * S[j + 1] + dx * b.y;
+                S[j + 2] = fast_exp2(dt * A[j + 2]) * S[j + 2] + dx * b.z;
+                S[j + 3] = fast_exp2(dt * A[j + 3]) * S[j + 3] + dx * b.w;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < SS_PER_THREAD; ++j) {
+                const int n = part + j * lanes;
+                if (n < n_state) S[j] = fast_exp2(dt * A[j]) * S[j] + dx * __ldg(B + n);
+            }
         }
     }
 #pragma unroll
@@ -237,7 +300,7 @@ selective_scan_sliced_kernel(const TX* __restrict__ x, const float* __restrict__
         for (int s = 0; s < TS; ++s) {
             const float from_zero = s_end[s][lx][j];
             s_end[s][lx][j] = h;
-            h = expf(A[j] * s_dt[s][lx]) * h + from_zero;
+            h = fast_exp2(A[j] * s_dt[s][lx]) * h + from_zero;
         }
     }
     __syncthreads();
@@ -251,12 +314,25 @@ selective_scan_sliced_kernel(const TX* __restrict__ x, const float* __restrict__
         const float* B = proj + (long long)t * proj_ld + b_col;
         const float* C = proj + (long long)t * proj_ld + c_col;
         float y = 0.f;
+        if (lanes == 1) {
 #pragma unroll
-        for (int j = 0; j < SS_PER_THREAD; ++j) {
-            const int n = part + j * lanes;
-            if (n < n_state) {
-                S[j] = expf(dt * A[j]) * S[j] + dx * __ldg(B + n);
-                y = fmaf(S[j], __ldg(C + n), y);
+            for (int j = 0; j < SS_PER_THREAD; j += 4) {
+                if (j >= n_state) break;
+                const float4 b = row_quad(B, j, n_state, quads), cq = row_quad(C, j, n_state, quads);
+                S[j] = fast_exp2(dt * A[j]) * S[j] + dx * b.x;
+                S[j + 1] = fast_exp2(dt * A[j + 1]) * S[j + 1] + dx * b.y;
+                S[j + 2] = fast_exp2(dt * A[j + 2]) * S[j + 2] + dx * b.z;
+                S[j + 3] = fast_exp2(dt * A[j + 3]) * S[j + 3] + dx * b.w;
+                y = fmaf(S[j], cq.x, fmaf(S[j + 1], cq.y, fmaf(S[j + 2], cq.z, fmaf(S[j + 3], cq.w, y))));
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < SS_PER_THREAD; ++j) {
+                const int n = part + j * lanes;
+                if (n < n_state) {
+                    S[j] = fast_exp2(dt * A[j]) * S[j] + dx * __ldg(B + n);
+                    y = fmaf(S[j], __ldg(C + n), y);
+                }
             }
         }
         for (int o = lanes >> 1; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);

@@ -68,26 +68,27 @@ gemm_simt_kernel(const TA* __restrict__ A, long long lda, const TW* __restrict__
 
 // Row strides lda/ldw/ldc are in elements.
 
-// A product with few output columns (a router, a gate of one number a token): a warp owns one row of A and up to SKINNY_NG
-// columns at a time; its lanes stride over k, so every load is a run of 32 consecutive elements, and the lanes' sums are
-// added in a fixed order.  A row's result does not depend on M either.
-constexpr int SKINNY_N = 32, SKINNY_NG = 8;
+// A product with few output columns (a router, a gate of one number a token): a block of four warps owns one row of A and
+// up to SKINNY_NG columns at a time; its threads stride over k, so every load is a run of consecutive elements and many are
+// under way at once, and the threads' sums are added in a fixed order.  A row's result does not depend on M either.
+constexpr int SKINNY_N = 32, SKINNY_NG = 16, SKINNY_THREADS = 128;
 
 template <typename TA, typename TW, typename TC>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(SKINNY_THREADS)
 gemm_skinny_kernel(const TA* __restrict__ A, long long lda, const TW* __restrict__ W, long long ldw, TC* __restrict__ C, long long ldc,
                    int M, int N, int K)
 {
+    __shared__ float part[SKINNY_THREADS / 32][SKINNY_NG];
     pdl_enter();
-    const int lane = threadIdx.x & 31;
-    const long long m = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (m >= M) return;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const long long m = blockIdx.x;
     const TA* a = A + m * lda;
     for (int n0 = 0; n0 < N; n0 += SKINNY_NG) {
         float acc[SKINNY_NG];
 #pragma unroll
         for (int j = 0; j < SKINNY_NG; ++j) acc[j] = 0.f;
-        for (int k = lane; k < K; k += 32) {
+#pragma unroll 2
+        for (int k = threadIdx.x; k < K; k += SKINNY_THREADS) {
             const float av = to_f32(a[k]);
 #pragma unroll
             for (int j = 0; j < SKINNY_NG; ++j)
@@ -96,8 +97,16 @@ gemm_skinny_kernel(const TA* __restrict__ A, long long lda, const TW* __restrict
 #pragma unroll
         for (int j = 0; j < SKINNY_NG; ++j) {
             const float sum = warp_sum(acc[j]);
-            if (lane == 0 && n0 + j < N) C[m * ldc + n0 + j] = from_f32<TC>(sum);
+            if (lane == 0) part[warp][j] = sum;
         }
+        __syncthreads();
+        if (threadIdx.x < SKINNY_NG && n0 + threadIdx.x < N) {
+            float sum = 0.f;
+#pragma unroll
+            for (int w = 0; w < SKINNY_THREADS / 32; ++w) sum += part[w][threadIdx.x];
+            C[m * ldc + n0 + threadIdx.x] = from_f32<TC>(sum);
+        }
+        __syncthreads();
     }
 }
 
@@ -111,7 +120,7 @@ extern "C" int spy_gemm_simt(const void* A, int a_dtype, long long lda, const vo
         SPY_DISPATCH_DTYPE(a_dtype, TA, {
             SPY_DISPATCH_DTYPE(w_dtype, TW, {
                 SPY_DISPATCH_DTYPE(c_dtype, TC, {
-                    spy_launch(gemm_skinny_kernel<TA, TW, TC>, dim3((unsigned)(((long long)M + 3) / 4)), dim3(128), 0, stream, (const TA*)A, lda,
+                    spy_launch(gemm_skinny_kernel<TA, TW, TC>, dim3((unsigned)M), dim3(SKINNY_THREADS), 0, stream, (const TA*)A, lda,
                                (const TW*)W, ldw, (TC*)C, ldc, M, N, K);
                 })
             })
