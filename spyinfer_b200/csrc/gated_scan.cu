@@ -243,6 +243,7 @@ selective_scan_sliced_kernel(const TX* __restrict__ x, const float* __restrict__
 {
     __shared__ float s_end[TS][32][SS_PER_THREAD + 1];
     __shared__ float s_dt[TS][32];
+    __shared__ __align__(16) float s_bc[TS][32];            // a slice's current token: B in the first half, C in the second
     pdl_enter();
     const int lx = threadIdx.x, ts = threadIdx.y, seq = blockIdx.y;
     const int idx = blockIdx.x * 32 + lx;
@@ -252,7 +253,6 @@ selective_scan_sliced_kernel(const TX* __restrict__ x, const float* __restrict__
     const int per = (L + TS - 1) / TS;
     const int t0 = start + min(ts * per, L), t1 = start + min((ts + 1) * per, L);
     const bool live = c < inner;
-    const bool quads = lanes == 1 && n_state % 4 == 0 && ((proj_ld | b_col | c_col) & 3) == 0;      // B and C rows by 16-byte loads
     const int cc = live ? c : 0;
     float A[SS_PER_THREAD], S[SS_PER_THREAD];
     float* st = state + ((long long)state_slot[seq] * inner + cc) * n_state;
@@ -264,23 +264,38 @@ selective_scan_sliced_kernel(const TX* __restrict__ x, const float* __restrict__
     }
     const float bias = live ? to_f32(dt_bias[cc]) : 0.f, D = live ? to_f32(d_skip[cc]) : 0.f;
     float sum_dt = 0.f;
+    // what the next step reads, fetched while the current one is computed; with one thread a channel the token's B and C rows
+    // (zeros past the last state) come in by one load of the warp and go round through shared memory
+    float pre_n = 0.f, x_n = 0.f, z_n = 0.f, bc_n = 0.f;
+    auto fetch = [&](int t, bool gate) {
+        if (t >= t1) return;
+        pre_n = live ? dt_pre[(long long)t * inner + cc] : 0.f;
+        x_n = live ? to_f32(x[(long long)t * inner + cc]) : 0.f;
+        if (gate) z_n = live ? z[(long long)t * z_ld + cc] : 0.f;
+        if (lanes == 1) bc_n = (lx & 15) < n_state ? __ldg(proj + (long long)t * proj_ld + (lx < 16 ? b_col : c_col) + (lx & 15)) : 0.f;
+    };
+    fetch(t0, false);
     for (int t = t0; t < t1; ++t) {
-        const float pre = live ? dt_pre[(long long)t * inner + cc] + bias : 0.f;
+        const float pre = pre_n + bias, xv = x_n, bc = bc_n;
+        fetch(t + 1, false);
         const float dt = pre > 20.f ? pre : log1pf(expf(pre));
-        const float dx = dt * (live ? to_f32(x[(long long)t * inner + cc]) : 0.f);
-        const float* B = proj + (long long)t * proj_ld + b_col;
+        const float dx = dt * xv;
         sum_dt += dt;
-        if (lanes == 1) {                                        // the thread's states are a run: B by quads
+        if (lanes == 1) {
+            __syncwarp();
+            s_bc[ts][lx] = bc;
+            __syncwarp();
 #pragma unroll
             for (int j = 0; j < SS_PER_THREAD; j += 4) {
                 if (j >= n_state) break;
-                const float4 b = row_quad(B, j, n_state, quads);
+                const float4 b = *reinterpret_cast<const float4*>(&s_bc[ts][j]);
                 S[j] = fast_exp2(dt * A[j]) * S[j] + dx * b.x;
                 S[j + 1] = fast_exp2(dt * A[j + 1]) * S[j + 1] + dx * b.y;
                 S[j + 2] = fast_exp2(dt * A[j + 2]) * S[j + 2] + dx * b.z;
                 S[j + 3] = fast_exp2(dt * A[j + 3]) * S[j + 3] + dx * b.w;
             }
         } else {
+            const float* B = proj + (long long)t * proj_ld + b_col;
 #pragma unroll
             for (int j = 0; j < SS_PER_THREAD; ++j) {
                 const int n = part + j * lanes;
@@ -306,19 +321,21 @@ selective_scan_sliced_kernel(const TX* __restrict__ x, const float* __restrict__
     __syncthreads();
 #pragma unroll
     for (int j = 0; j < SS_PER_THREAD; ++j) S[j] = s_end[ts][lx][j];
+    fetch(t0, true);
     for (int t = t0; t < t1; ++t) {
-        const float pre = live ? dt_pre[(long long)t * inner + cc] + bias : 0.f;
+        const float pre = pre_n + bias, xv = x_n, zv = z_n, bc = bc_n;
+        fetch(t + 1, true);
         const float dt = pre > 20.f ? pre : log1pf(expf(pre));
-        const float xv = live ? to_f32(x[(long long)t * inner + cc]) : 0.f;
         const float dx = dt * xv;
-        const float* B = proj + (long long)t * proj_ld + b_col;
-        const float* C = proj + (long long)t * proj_ld + c_col;
         float y = 0.f;
         if (lanes == 1) {
+            __syncwarp();
+            s_bc[ts][lx] = bc;
+            __syncwarp();
 #pragma unroll
             for (int j = 0; j < SS_PER_THREAD; j += 4) {
                 if (j >= n_state) break;
-                const float4 b = row_quad(B, j, n_state, quads), cq = row_quad(C, j, n_state, quads);
+                const float4 b = *reinterpret_cast<const float4*>(&s_bc[ts][j]), cq = *reinterpret_cast<const float4*>(&s_bc[ts][16 + j]);
                 S[j] = fast_exp2(dt * A[j]) * S[j] + dx * b.x;
                 S[j + 1] = fast_exp2(dt * A[j + 1]) * S[j + 1] + dx * b.y;
                 S[j + 2] = fast_exp2(dt * A[j + 2]) * S[j + 2] + dx * b.z;
@@ -326,6 +343,8 @@ selective_scan_sliced_kernel(const TX* __restrict__ x, const float* __restrict__
                 y = fmaf(S[j], cq.x, fmaf(S[j + 1], cq.y, fmaf(S[j + 2], cq.z, fmaf(S[j + 3], cq.w, y))));
             }
         } else {
+            const float* B = proj + (long long)t * proj_ld + b_col;
+            const float* C = proj + (long long)t * proj_ld + c_col;
 #pragma unroll
             for (int j = 0; j < SS_PER_THREAD; ++j) {
                 const int n = part + j * lanes;
@@ -334,11 +353,10 @@ selective_scan_sliced_kernel(const TX* __restrict__ x, const float* __restrict__
                     y = fmaf(S[j], __ldg(C + n), y);
                 }
             }
+            for (int o = lanes >> 1; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
         }
-        for (int o = lanes >> 1; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
         if (live && part == 0) {
             y = fmaf(D, xv, y);
-            const float zv = z[(long long)t * z_ld + cc];
             out[(long long)t * inner + cc] = from_f32<TO>(y * (zv * sigmoidf_(zv)));
         }
     }
