@@ -106,14 +106,24 @@ constexpr int SWIGLU_STAGE_LD = 66;   // bf16 elements between the tokens of a s
 // the rest of a tile's read-out (64 tokens: 4.0 against 1.5 microseconds).  A gate below -87 gives
 // g / inf = -0, the limit.  The 32-bit path has its own SwiGLU kernel with the accurate functions.
 __device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
+// the tanh form of gelu on the gate (EPI == 3), with the hardware tanh (error below 2^-10, inside the bfloat16 result's rounding)
+__device__ __forceinline__ float gelu_tanh_mul(float g, float u)
+{
+    float t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.7978845608028654f * fmaf(0.044715f * g, g * g, g)));
+    return 0.5f * g * (1.0f + t) * u;
+}
+// EPI 1 and 3 are the gated epilogues: act(gate) * up over alternating rows
+__host__ __device__ constexpr bool gated_epilogue(int epi) { return epi == 1 || epi == 3; }
+template <int EPI> __device__ __forceinline__ float gated_mul(float g, float u) { return EPI == 3 ? gelu_tanh_mul(g, u) : silu_mul(g, u); }
 // the square of relu: the activation of a feed-forward without a gate (EPI == 2)
 __device__ __forceinline__ float relu_squared(float v) { const float p = fmaxf(v, 0.f); return p * p; }
 
 // X: the weights [x_rows, K] in the instruction's M slot; Y: the tokens [y_rows, K] in its N slot;
 // out[y, x] (row stride ld).  splits > 1: out is the float scratch [splits][rows][ld] and TC is float.
 // EPI == 2: the result is relu(x)^2 of the product, element by element, in the plain layout; K is not split.
-// EPI == 1 (SwiGLU): the weight's rows alternate gate, up, gate, up, ...; the kernel stores
-// silu(gate) * up, half as many output columns (ld counts those); one pass over K only.
+// EPI == 1 (SwiGLU) and EPI == 3 (the same with the tanh form of gelu): the weight's rows alternate gate, up, gate, up, ...; the kernel stores
+// act(gate) * up, half as many output columns (ld counts those); one pass over K only.
 template <int BN, typename TC, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 2)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y, TC* __restrict__ out,
@@ -249,7 +259,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 const int cols = BN >= 32 ? 32 : BN;
                 const int y = y0 + c;
-                if constexpr (EPI == 1) {
+                if constexpr (gated_epilogue(EPI)) {
                     // lanes 2i and 2i + 1 hold gate row and up row of output x / 2 for every token.  Two tokens
                     // at a time: the even lane sends the second token's gate and finishes the first token, the
                     // odd lane sends the first token's up and finishes the second, so every lane computes.
@@ -263,7 +273,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                         if (j < cols) {
                             const float a = __uint_as_float(r[j]), b = __uint_as_float(r[j + 1]);
                             const float got = __shfl_xor_sync(0xffffffffu, odd ? a : b, 1);
-                            const float v = silu_mul(odd ? got : a, odd ? b : got);
+                            const float v = gated_mul<EPI>(odd ? got : a, odd ? b : got);
                             staged[(c + j + (odd ? 1 : 0)) * SWIGLU_STAGE_LD + ((quarter * 32 + lane) >> 1)] = __float2bfloat16_rn(v);
                         }
                     }
@@ -281,7 +291,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                     }
                 }
             }
-            if constexpr (EPI != 1 && BN >= 32) {
+            if constexpr (!gated_epilogue(EPI) && BN >= 32) {
                 epilogue_barrier();
                 const float* staged = reinterpret_cast<const float*>(tiles);
                 const int e = quarter * 32 + lane;
@@ -310,7 +320,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                     }
                 }
             }
-            if constexpr (EPI == 1) {
+            if constexpr (gated_epilogue(EPI)) {
                 // rows of the staged tile to the output, 4 bytes a lane where the row allows it
                 epilogue_barrier();
                 const bf16* staged = reinterpret_cast<const bf16*>(tiles);
@@ -364,10 +374,10 @@ template <typename TC, int EPI>
 __device__ __forceinline__ void store_chunk_normal(TC* base, long long ld, int x, int y, int x_rows, int y_rows, const uint32_t (&r)[32])
 {
     if (x >= x_rows || y >= y_rows) return;
-    if constexpr (EPI == 1) {
+    if constexpr (gated_epilogue(EPI)) {
         uint32_t o[16];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) o[j] = __float_as_uint(silu_mul(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1])));
+        for (int j = 0; j < 16; ++j) o[j] = __float_as_uint(gated_mul<EPI>(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1])));
         TC* dst = base + (size_t)x * ld + y / 2;
         const int valid = min(16, (y_rows - y) / 2);
         if (valid >= 16 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0 && sizeof(TC) == 2) {
@@ -1255,6 +1265,7 @@ extern "C" int spy_gemm_tcgen05_plan(int M, int N, int K, long long scratch_limi
 // apart.  scratch: float buffer of at least the plan's size (may be null when it is 0).
 // epilogue 1 (SwiGLU): W's rows alternate gate and up rows, C is [M, N / 2], K is not split.
 // epilogue 2: C = relu(A W^T)^2 element by element, K is not split.
+// epilogue 3: as 1 with gelu_tanh(gate) * up.
 // defer_reduce: when the plan splits K, the partial products stay in scratch as
 // [splits][M][N] floats for the consumer to sum (C is not written); *splits_used tells.
 // next_weights / next_bytes (may be null / 0; used by products of up to 256 tokens only): memory that a
@@ -1274,9 +1285,9 @@ extern "C" int spy_gemm_tcgen05_ex(const void* A, long long lda, const void* W, 
     if (lda % 8 != 0 || ldw % 8 != 0) SPY_FAIL("gemm_tcgen05: row strides %lld/%lld must be multiples of 8 elements", lda, ldw);
     if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(W) & 15)) SPY_FAIL("gemm_tcgen05: operands must be 16-byte aligned");
     if (c_dtype != SPY_F32 && c_dtype != SPY_BF16) SPY_FAIL("gemm_tcgen05: unknown output dtype code %d", c_dtype);
-    if (epilogue < 0 || epilogue > 2) SPY_FAIL("gemm_tcgen05: unknown epilogue %d", epilogue);
+    if (epilogue < 0 || epilogue > 3) SPY_FAIL("gemm_tcgen05: unknown epilogue %d", epilogue);
     if (epilogue == 2 && c_dtype != SPY_BF16) SPY_FAIL("gemm_tcgen05: the relu-squared epilogue needs bfloat16 output");
-    if (epilogue == 1 && (N % 2 != 0 || c_dtype != SPY_BF16)) SPY_FAIL("gemm_tcgen05: the SwiGLU epilogue needs an even N and bfloat16 output");
+    if ((epilogue == 1 || epilogue == 3) && (N % 2 != 0 || c_dtype != SPY_BF16)) SPY_FAIL("gemm_tcgen05: a gated epilogue needs an even N and bfloat16 output");
     Plan plan = make_plan(M, N, K, epilogue == 0);
     if (plan.splits > 1 && (scratch == nullptr || (long long)plan.splits * M * N > scratch_floats)) plan = make_plan(M, N, K, false);
     const int splits = plan.splits;
@@ -1311,6 +1322,7 @@ extern "C" int spy_gemm_tcgen05_ex(const void* A, long long lda, const void* W, 
             SPY_CUDA(cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<float, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PAIR_SMEM));
             SPY_CUDA(cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<bf16, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PAIR_SMEM));
             SPY_CUDA(cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<bf16, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PAIR_SMEM));
+            SPY_CUDA(cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<bf16, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PAIR_SMEM));
             const int sms = spy_sm_count();
             cudaLaunchConfig_t cfg = {};
             cfg.gridDim = dim3(sms / 2 * 2);
@@ -1363,6 +1375,9 @@ extern "C" int spy_gemm_tcgen05_ex(const void* A, long long lda, const void* W, 
         else if (epilogue == 1)
             spy_launch_cluster(gemm_tcgen05_pair_kernel<bf16, 1>, dim3(2 * clusters), dim3(NUM_THREADS), PAIR_SMEM, stream, 2u, mx, my_half, (bf16*)C, ldc,
                                M, N, k_blocks, x_tiles, (int)num_tiles, 1, k_blocks, 0LL, tail_tiles, tail_p, tail_x, scratch, status);
+        else if (epilogue == 3)
+            spy_launch_cluster(gemm_tcgen05_pair_kernel<bf16, 3>, dim3(2 * clusters), dim3(NUM_THREADS), PAIR_SMEM, stream, 2u, mx, my_half, (bf16*)C, ldc,
+                               M, N, k_blocks, x_tiles, (int)num_tiles, 1, k_blocks, 0LL, tail_tiles, tail_p, tail_x, scratch, status);
         else if (c_dtype == SPY_F32)
             spy_launch_cluster(gemm_tcgen05_pair_kernel<float, 0>, dim3(2 * clusters), dim3(NUM_THREADS), PAIR_SMEM, stream, 2u, mx, my_half, (float*)C, ldc,
                                M, N, k_blocks, x_tiles, (int)num_tiles, 1, k_blocks, 0LL, tail_tiles, tail_p, tail_x, scratch, status);
@@ -1405,12 +1420,16 @@ extern "C" int spy_gemm_tcgen05_ex(const void* A, long long lda, const void* W, 
             SPY_CUDA(cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<float, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WideTile::SMEM));
             SPY_CUDA(cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<bf16, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WideTile::SMEM));
             SPY_CUDA(cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<bf16, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WideTile::SMEM));
+            SPY_CUDA(cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<bf16, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WideTile::SMEM));
         }
         if (epilogue == 2)
             spy_launch(gemm_tcgen05_persistent_kernel<bf16, 2>, dim3(grid), dim3(NUM_THREADS), WideTile::SMEM, stream, mx, my, (bf16*)C, ldc, M, N,
                        k_blocks, x_tiles, (int)num_tiles, stream_tiles, per_block, scratch, status);
         else if (epilogue == 1)
             spy_launch(gemm_tcgen05_persistent_kernel<bf16, 1>, dim3(grid), dim3(NUM_THREADS), WideTile::SMEM, stream, mx, my, (bf16*)C, ldc, M, N,
+                       k_blocks, x_tiles, (int)num_tiles, stream_tiles, per_block, scratch, status);
+        else if (epilogue == 3)
+            spy_launch(gemm_tcgen05_persistent_kernel<bf16, 3>, dim3(grid), dim3(NUM_THREADS), WideTile::SMEM, stream, mx, my, (bf16*)C, ldc, M, N,
                        k_blocks, x_tiles, (int)num_tiles, stream_tiles, per_block, scratch, status);
         else if (c_dtype == SPY_F32)
             spy_launch(gemm_tcgen05_persistent_kernel<float, 0>, dim3(grid), dim3(NUM_THREADS), WideTile::SMEM, stream, mx, my, (float*)C, ldc, M, N,
@@ -1426,6 +1445,7 @@ extern "C" int spy_gemm_tcgen05_ex(const void* A, long long lda, const void* W, 
 #define SPY_LAUNCH(BN_)                                                                                                             \
     rc = epilogue == 2 ? launch<BN_, bf16, 2>(mx, my, out, ld, split_stride, x_rows, y_rows, k_blocks, splits, plan.tile_rows, status, stream, next_weights, next_bytes)   \
          : epilogue == 1 ? launch<BN_, bf16, 1>(mx, my, out, ld, split_stride, x_rows, y_rows, k_blocks, splits, plan.tile_rows, status, stream, next_weights, next_bytes)   \
+         : epilogue == 3 ? launch<BN_, bf16, 3>(mx, my, out, ld, split_stride, x_rows, y_rows, k_blocks, splits, plan.tile_rows, status, stream, next_weights, next_bytes)   \
          : f32_out     ? launch<BN_, float, 0>(mx, my, out, ld, split_stride, x_rows, y_rows, k_blocks, splits, plan.tile_rows, status, stream, next_weights, next_bytes)  \
                        : launch<BN_, bf16, 0>(mx, my, out, ld, split_stride, x_rows, y_rows, k_blocks, splits, plan.tile_rows, status, stream, next_weights, next_bytes)
     if (bn == 16) SPY_LAUNCH(16);

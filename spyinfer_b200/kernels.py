@@ -925,7 +925,7 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] =
     bfloat16 or float32 output.  K must be a multiple of 8.
 
     ``epilogue="swiglu"``: ``w``'s rows alternate gate and up rows and the result is
-    ``silu(gate) * up``, ``[M, N / 2]``.  ``epilogue="relu2"``: the result is ``relu(a @ w^T)^2`` (bfloat16 output).  ``defer=True``: when the kernel splits K, the float32
+    ``silu(gate) * up``, ``[M, N / 2]``; ``epilogue="geglu_tanh"``: the same with the tanh form of gelu on the gate.  ``epilogue="relu2"``: the result is ``relu(a @ w^T)^2`` (bfloat16 output).  ``defer=True``: when the kernel splits K, the float32
     partial products are returned unsummed as ``[splits, M, N]`` for a consumer that adds them
     (``rmsnorm``'s delta, ``qk_rope_store``'s input); otherwise the result is ``[M, N]``.
     ``prefetch``: a tensor that a later kernel will read (the next product's weights); with up to 256
@@ -937,11 +937,11 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] =
     N = w.shape[0]
     if w.shape[1] != K:
         raise KernelError(f"gemm: shapes do not fit: input {tuple(a.shape)}, weight {tuple(w.shape)}")
-    if epilogue not in (None, "swiglu", "relu2"):
+    if epilogue not in (None, "swiglu", "relu2", "geglu_tanh"):
         raise KernelError(f"gemm: unknown epilogue {epilogue!r}")
     if epilogue == "relu2" and (out_dtype or torch.bfloat16) != torch.bfloat16:
         raise KernelError("gemm: the relu2 epilogue writes bfloat16")
-    n_out = N // 2 if epilogue == "swiglu" else N
+    n_out = N // 2 if epilogue in ("swiglu", "geglu_tanh") else N
     if status is None:
         status = status_word(a.device)
     lib = build.load("gemm_tcgen05")
@@ -970,7 +970,7 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] =
     scratch = _scratch(a.device)
     _call("gemm_tcgen05", "spy_gemm_tcgen05_ex", _ptr(a), ctypes.c_longlong(K), _ptr(w), ctypes.c_longlong(K), _ptr(out),
           _code(out, "gemm output"), ctypes.c_longlong(n_out), M, N, K, _ptr(scratch), ctypes.c_longlong(scratch.numel()),
-          {None: 0, "swiglu": 1, "relu2": 2}[epilogue], 0, None, _ptr(status), _stream(), pf_ptr, ctypes.c_longlong(pf_bytes))
+          {None: 0, "swiglu": 1, "relu2": 2, "geglu_tanh": 3}[epilogue], 0, None, _ptr(status), _stream(), pf_ptr, ctypes.c_longlong(pf_bytes))
     return out
 
 

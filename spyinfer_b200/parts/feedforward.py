@@ -94,10 +94,10 @@ class GatedMLP(FeedForward):
         gate, up = tensors[p + n["gate"]], tensors[p + n["up"]]
         if gate.dtype != up.dtype:
             gate, up = gate.float(), up.float()
-        self.fused = (self.ctx.dtype == torch.bfloat16 and gate.dtype == torch.bfloat16 and self.activation == "silu"
+        self.fused = (self.ctx.dtype == torch.bfloat16 and gate.dtype == torch.bfloat16 and self.activation in ("silu", "gelu_tanh")
                       and kernels.tensor_core_gemm_takes(2 * self.inter, self.hidden))
         if self.fused:
-            # rows alternate gate_i, up_i: the tensor-core product applies SwiGLU in its epilogue
+            # rows alternate gate_i, up_i: the tensor-core product applies act(gate) * up in its epilogue
             self.gate_up = Linear(torch.stack([gate, up], dim=1).reshape(2 * self.inter, self.hidden).contiguous(), self.ctx.dtype)
         else:
             self.gate_up = Linear(torch.cat([gate, up], dim=0).contiguous(), self.ctx.dtype)
@@ -112,7 +112,7 @@ class GatedMLP(FeedForward):
 
     def forward(self, x):
         if self.fused:
-            return self.down(self.gate_up(x, epilogue="swiglu"), defer=self.defer_output)
+            return self.down(self.gate_up(x, epilogue="swiglu" if self.activation == "silu" else "geglu_tanh"), defer=self.defer_output)
         gu = self.gate_up(x)
         z = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
         if self.activation == "silu":

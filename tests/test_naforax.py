@@ -558,6 +558,24 @@ def test_the_two_maps_are_subtracted_normed_and_gated(dtype, heads, vdim, hd):
 
 
 @gpu
+@pytest.mark.parametrize("M", [1, 8, 40, 100, 128, 200, 300, 640, 1200, 2048])
+@pytest.mark.parametrize("N,K", [(320, 136), (4096, 1024), (6400, 2048)])
+def test_product_with_the_gelu_gate_in_its_epilogue(M, N, K):
+    """The tensor-core product over alternating gate and up rows hands out ``gelu_tanh(gate) * up``, on every kernel that the
+    number of tokens selects."""
+    from spyinfer_b200 import kernels
+
+    g = torch.Generator().manual_seed(M + N)
+    a = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (2.0 * torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    out = kernels.gemm_tcgen05(a.cuda(), w.cuda(), epilogue="geglu_tanh")
+    prod = a.double() @ w.double().T
+    want = P.gelu_tanh(prod[:, 0::2]) * prod[:, 1::2]
+    assert out.dtype == torch.bfloat16 and tuple(out.shape) == (M, N // 2)
+    assert torch.allclose(out.float().cpu().double(), want, atol=2e-2, rtol=2e-2)
+
+
+@gpu
 def test_gelu_gate_logit_cap_and_what_goes_into_the_stream_ahead_of_a_pass():
     from spyinfer_b200 import kernels
 
