@@ -16,7 +16,7 @@ constexpr int MOE_MAX_EXPERTS = 1024;
 template <typename TA, typename TO>
 __global__ void moe_activation_kernel(const TA* __restrict__ gu, long long gu_ld, const float* __restrict__ logits, long long logits_ld,
                                       TO* __restrict__ y, long long y_ld, int experts, int top, int ff, float limit, int shared_ff, float shared_limit,
-                                      float alpha, float* __restrict__ weights_out)
+                                      float alpha, float* __restrict__ weights_out, int vec)
 {
     extern __shared__ float w_s[];                 // experts + 1 weights
     __shared__ float scratch[33];
@@ -49,6 +49,34 @@ __global__ void moe_activation_kernel(const TA* __restrict__ gu, long long gu_ld
     const TA* g_row = gu + (long long)t * gu_ld;
     TO* y_row = y + (long long)t * y_ld;
     const int routed = experts * ff;
+    if constexpr (sizeof(TA) == 2 && sizeof(TO) == 2) {
+        if (vec) {
+            // eight elements (16 bytes) a thread and step; a run of eight lies within one expert, and an expert that the token did
+            // not choose costs one store of zeros and no load
+            for (int i = tid * 8; i < routed + shared_ff; i += blockDim.x * 8) {
+                float w, lim;
+                const TA* src;
+                int j, n;
+                if (i < routed) { const int e = i / ff; j = i - e * ff; n = ff; w = w_s[experts + 1 + e]; lim = limit; src = g_row + (long long)e * 2 * ff; }
+                else { j = i - routed; n = shared_ff; w = w_s[experts]; lim = shared_limit; src = g_row + (long long)routed * 2; }
+                uint4 packed = make_uint4(0u, 0u, 0u, 0u);
+                if (w != 0.f) {
+                    const uint4 gq = *reinterpret_cast<const uint4*>(src + j), uq = *reinterpret_cast<const uint4*>(src + n + j);
+                    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gq);
+                    const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uq);
+                    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const float ga = fminf(__low2float(g2[q]), lim), gb = fminf(__high2float(g2[q]), lim);
+                        const float ua = fminf(fmaxf(__low2float(u2[q]), -lim), lim), ub = fminf(fmaxf(__high2float(u2[q]), -lim), lim);
+                        o2[q] = __floats2bfloat162_rn(w * (ga / (1.0f + expf(-alpha * ga))) * (ua + 1.0f), w * (gb / (1.0f + expf(-alpha * gb))) * (ub + 1.0f));
+                    }
+                }
+                *reinterpret_cast<uint4*>(y_row + i) = packed;
+            }
+            return;
+        }
+    }
     for (int i = tid; i < routed + shared_ff; i += blockDim.x) {
         float w, lim;
         const TA* src;
@@ -76,10 +104,12 @@ extern "C" int spy_moe_activation(const void* gu, int gu_dtype, long long gu_ld,
     if (experts <= 0 || experts > MOE_MAX_EXPERTS || top <= 0 || top > experts || ff <= 0 || shared_ff < 0)
         SPY_FAIL("moe_activation: %d experts (at most %d), top %d, expert size %d, shared size %d", experts, MOE_MAX_EXPERTS, top, ff, shared_ff);
     const size_t smem = (size_t)(2 * experts + 2) * sizeof(float);
+    const int vec = gu_dtype == SPY_BF16 && y_dtype == SPY_BF16 && ff % 8 == 0 && shared_ff % 8 == 0 && gu_ld % 8 == 0 && y_ld % 8 == 0
+                    && ((reinterpret_cast<uintptr_t>(gu) | reinterpret_cast<uintptr_t>(y)) & 15) == 0;
     SPY_DISPATCH_DTYPE(gu_dtype, TA, {
         SPY_DISPATCH_DTYPE(y_dtype, TO, {
             spy_launch(moe_activation_kernel<TA, TO>, dim3(tokens), dim3(256), smem, stream, (const TA*)gu, gu_ld, logits, logits_ld, (TO*)y, y_ld,
-                       experts, top, ff, limit, shared_ff, shared_limit, alpha, weights_out);
+                       experts, top, ff, limit, shared_ff, shared_limit, alpha, weights_out, vec);
         })
     })
     SPY_CHECK_LAUNCH("moe_activation");
