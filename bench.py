@@ -674,7 +674,8 @@ def naforax_workload(args) -> int:
                     rate(block, "group_norm.spy_group_norm", nbytes=float(2 * layers) * rows * W * (4 + 4 + 4 + 2))
                     rate(block, "time_conv.spy_time_conv", nbytes=float(2 * layers) * rows * W * 4 + float(n_scan) * rows * z["inner"] * 6)
                     cols = z["experts"] * z["expert_ff"] + z["shared_ff"]
-                    rate(block, "moe.spy_moe_activation", nbytes=float(n_moe) * rows * cols * 6)
+                    # reads the chosen experts' and the shared expert's gate and up, writes every expert's columns (zeros for the others)
+                    rate(block, "moe.spy_moe_activation", nbytes=float(n_moe) * rows * ((z["top"] * z["expert_ff"] + z["shared_ff"]) * 4 + cols * 2))
                     rate(block, "gated_scan.spy_mingru_scan", nbytes=float(n_gru) * (rows * z["gru"] * (12 + 2) + (64 * z["gru"] * 8 if rows == 64 else 0)))
                     rate(block, "gated_scan.spy_selective_scan",
                          nbytes=float(n_scan) * (rows * z["inner"] * (2 + 4 + 4 + 2) + (64 * z["inner"] * z["state"] * 8 if rows == 64 else 0)))

@@ -62,13 +62,24 @@ mingru_scan_sliced_kernel(const float* __restrict__ proj, long long ld, int z_co
     const float bz = z_bias != nullptr ? to_f32(z_bias[cc]) : 0.f, bx = x_bias != nullptr ? to_f32(x_bias[cc]) : 0.f;
     float A = 1.f, B = 0.f;
     const float* p = proj + (long long)t0 * ld + cc;
-#pragma unroll 4
-    for (int t = t0; t < t1; ++t, p += ld) {
-        const float z = sigmoidf_(p[z_col] + bz);
-        const float u = p[x_col] + bx;
-        const float cand = u >= 0.f ? u + 0.5f : sigmoidf_(u);
-        A *= 1.0f - z;
-        B = (1.0f - z) * B + z * cand;
+    // four tokens' loads are under way before the first of them is used
+    for (int t = t0; t < t1; t += 4, p += 4 * ld) {
+        float pz[4], px[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const bool in = t + i < t1;
+            pz[i] = in ? p[(long long)i * ld + z_col] : 0.f;
+            px[i] = in ? p[(long long)i * ld + x_col] : 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            if (t + i >= t1) break;
+            const float z = sigmoidf_(pz[i] + bz);
+            const float u = px[i] + bx;
+            const float cand = u >= 0.f ? u + 0.5f : sigmoidf_(u);
+            A *= 1.0f - z;
+            B = (1.0f - z) * B + z * cand;
+        }
     }
     sa[ts][lane] = A;
     sb[ts][lane] = B;
@@ -86,14 +97,24 @@ mingru_scan_sliced_kernel(const float* __restrict__ proj, long long ld, int z_co
     __syncthreads();
     float S = sb[ts][lane];
     p = proj + (long long)t0 * ld + cc;
-#pragma unroll 4
-    for (int t = t0; t < t1; ++t, p += ld) {
-        const float z = sigmoidf_(p[z_col] + bz);
-        const float u = p[x_col] + bx;
-        const float cand = u >= 0.f ? u + 0.5f : sigmoidf_(u);
-        const float g = p[g_col];
-        S = (1.0f - z) * S + z * cand;
-        if (live) out[(long long)t * width + c] = from_f32<TO>(S * (g * sigmoidf_(g)));
+    for (int t = t0; t < t1; t += 4, p += 4 * ld) {
+        float pz[4], px[4], pg[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const bool in = t + i < t1;
+            pz[i] = in ? p[(long long)i * ld + z_col] : 0.f;
+            px[i] = in ? p[(long long)i * ld + x_col] : 0.f;
+            pg[i] = in ? p[(long long)i * ld + g_col] : 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            if (t + i >= t1) break;
+            const float z = sigmoidf_(pz[i] + bz);
+            const float u = px[i] + bx;
+            const float cand = u >= 0.f ? u + 0.5f : sigmoidf_(u);
+            S = (1.0f - z) * S + z * cand;
+            if (live) out[(long long)(t + i) * width + c] = from_f32<TO>(S * (pg[i] * sigmoidf_(pg[i])));
+        }
     }
     if (live && t0 < t1 && t1 == start + L) *st = S;          // the slice that holds the run's last token leaves the state
 }
