@@ -115,3 +115,224 @@ extern "C" int spy_moe_activation(const void* gu, int gu_dtype, long long gu_ld,
     SPY_CHECK_LAUNCH("moe_activation");
     return 0;
 }
+
+// ---- the routed form, for steps of many tokens ------------------------------------------------------------------------
+//
+// With many tokens a step, computing every expert for every token wastes experts / top of the products.  The routed form
+// sorts the (token, chosen expert) pairs by expert, gathers the tokens' rows in that order, runs each expert's products on
+// its own run of rows, and adds each token's `top` results up again in a fixed order.  The weights are the same as above
+// (moe_route repeats the softmax and the choice), so a token's result differs from the dense form by rounding only.
+
+// One warp a token (a block walks over tokens with a stride): the chosen experts in ascending order with their weights, the shared
+// expert's gate, and the experts' counts (added up per block in shared memory first, so few additions meet in global memory).
+__global__ void moe_route_kernel(const float* __restrict__ logits, long long logits_ld, int tokens, int experts, int top, int has_shared,
+                                 int* __restrict__ choice, float* __restrict__ choice_w, float* __restrict__ shared_w, int* __restrict__ counts)
+{
+    extern __shared__ float w_all[];               // experts floats a warp, then the block's counts
+    pdl_enter();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    int* hist = reinterpret_cast<int*>(w_all + (long long)nwarps * experts);
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) hist[e] = 0;
+    __syncthreads();
+    float* w_s = w_all + (long long)warp * experts;
+    for (long long t = (long long)blockIdx.x * nwarps + warp; t < tokens; t += (long long)gridDim.x * nwarps) {
+        const float* lg = logits + t * logits_ld;
+        float m = -INFINITY;
+        for (int e = lane; e < experts; e += 32) m = fmaxf(m, lg[e]);
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        float s = 0.f;
+        for (int e = lane; e < experts; e += 32) s += expf(lg[e] - m);
+        s = warp_sum(s);
+        __syncwarp();
+        for (int e = lane; e < experts; e += 32) w_s[e] = expf(lg[e] - m) / s;
+        __syncwarp();
+        int k_base = 0;
+        for (int e0 = 0; e0 < experts; e0 += 32) {
+            const int e = e0 + lane;
+            bool chosen = false;
+            float v = 0.f;
+            if (e < experts) {
+                v = w_s[e];
+                int ahead = 0;
+                for (int o = 0; o < experts; ++o) {
+                    const float x = w_s[o];
+                    ahead += (x > v || (x == v && o < e)) ? 1 : 0;
+                }
+                chosen = ahead < top;
+            }
+            const unsigned ballot = __ballot_sync(0xffffffffu, chosen);
+            if (chosen) {
+                const int k = k_base + __popc(ballot & ((1u << lane) - 1u));
+                choice[t * top + k] = e;
+                choice_w[t * top + k] = v;
+                atomicAdd(hist + e, 1);
+            }
+            k_base += __popc(ballot);
+        }
+        if (lane == 0 && has_shared) shared_w[t] = 1.0f / (1.0f + expf(-lg[experts]));
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < experts; e += blockDim.x)
+        if (hist[e] != 0) atomicAdd(counts + e, hist[e]);
+}
+
+// One block an expert: its rows' places, in the order of the tokens.  Each warp takes a run of the pairs, counts the expert's
+// pairs in it, and after a prefix over the warps' counts hands out the places.  offsets [experts + 1]; slot [tokens * top]: the
+// row of each (token, k); row_token, row_w [tokens * top]: each row's token and weight.
+__global__ void __launch_bounds__(1024)
+moe_slots_kernel(const int* __restrict__ choice, const float* __restrict__ choice_w, const int* __restrict__ counts, int pairs,
+                 int top, int experts, int* __restrict__ offsets, int* __restrict__ slot, int* __restrict__ row_token,
+                 float* __restrict__ row_w)
+{
+    __shared__ int warp_count[32];
+    __shared__ int first_row;
+    pdl_enter();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const int e = blockIdx.x;
+    const int per_warp = ((pairs + nwarps - 1) / nwarps + 31) / 32 * 32;
+    const int i_first = min(warp * per_warp, pairs), i_end = min(i_first + per_warp, pairs);
+    int mine_count = 0;
+    for (int i0 = i_first; i0 < i_end; i0 += 32) {
+        const int i = i0 + lane;
+        mine_count += __popc(__ballot_sync(0xffffffffu, i < i_end && choice[i] == e));
+    }
+    if (lane == 0) warp_count[warp] = mine_count;
+    if (warp == 0) {
+        int base = 0;
+        for (int o = lane; o < e; o += 32) base += counts[o];
+        for (int o = 16; o > 0; o >>= 1) base += __shfl_xor_sync(0xffffffffu, base, o);
+        if (lane == 0) {
+            first_row = base;
+            offsets[e] = base;
+            if (e == experts - 1) offsets[experts] = base + counts[e];
+        }
+    }
+    __syncthreads();
+    int base = first_row;
+    for (int w = 0; w < warp; ++w) base += warp_count[w];
+    for (int i0 = i_first; i0 < i_end; i0 += 32) {
+        const int i = i0 + lane;
+        const bool mine = i < i_end && choice[i] == e;
+        const unsigned ballot = __ballot_sync(0xffffffffu, mine);
+        if (mine) {
+            const int r = base + __popc(ballot & ((1u << lane) - 1u));
+            slot[i] = r;
+            row_token[r] = i / top;
+            row_w[r] = choice_w[i];
+        }
+        base += __popc(ballot);
+    }
+}
+
+// out[r] = in[row_token[r]]: rows of `len` elements of 2 bytes (bf16) or 4, copied 16 bytes at a time where the rows allow it.
+__global__ void gather_rows_kernel(const uint8_t* __restrict__ in, const int* __restrict__ row_token, uint8_t* __restrict__ out, long long row_bytes)
+{
+    pdl_enter();
+    const uint8_t* src = in + (long long)row_token[blockIdx.x] * row_bytes;
+    uint8_t* dst = out + (long long)blockIdx.x * row_bytes;
+    if ((row_bytes & 15) == 0) {
+        for (long long i = threadIdx.x * 16LL; i < row_bytes; i += blockDim.x * 16LL) *reinterpret_cast<uint4*>(dst + i) = *reinterpret_cast<const uint4*>(src + i);
+    } else {
+        for (long long i = threadIdx.x; i < row_bytes; i += blockDim.x) dst[i] = src[i];
+    }
+}
+
+// y[r, i] = w[r] * g * sigmoid(alpha g) * (u + 1) over rows of [gate (ff) | up (ff)], g = min(gate, limit), u = clamp(up, -limit, limit)
+template <typename TA, typename TO>
+__global__ void expert_activation_kernel(const TA* __restrict__ gu, long long gu_ld, const float* __restrict__ row_w, TO* __restrict__ y, long long y_ld,
+                                         int ff, float limit, float alpha, int vec)
+{
+    pdl_enter();
+    const long long r = blockIdx.x;
+    const float w = row_w[r];
+    const TA* src = gu + r * gu_ld;
+    TO* dst = y + r * y_ld;
+    if constexpr (sizeof(TA) == 2 && sizeof(TO) == 2) {
+        if (vec) {                                  // eight elements (16 bytes) a thread and step
+            for (int i = threadIdx.x * 8; i < ff; i += blockDim.x * 8) {
+                const uint4 gq = *reinterpret_cast<const uint4*>(src + i), uq = *reinterpret_cast<const uint4*>(src + ff + i);
+                const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gq);
+                const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uq);
+                uint4 packed;
+                __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float ga = fminf(__low2float(g2[q]), limit), gb = fminf(__high2float(g2[q]), limit);
+                    const float ua = fminf(fmaxf(__low2float(u2[q]), -limit), limit), ub = fminf(fmaxf(__high2float(u2[q]), -limit), limit);
+                    o2[q] = __floats2bfloat162_rn(w * (ga / (1.0f + expf(-alpha * ga))) * (ua + 1.0f), w * (gb / (1.0f + expf(-alpha * gb))) * (ub + 1.0f));
+                }
+                *reinterpret_cast<uint4*>(dst + i) = packed;
+            }
+            return;
+        }
+    }
+    for (int i = threadIdx.x; i < ff; i += blockDim.x) {
+        const float g = fminf(to_f32(src[i]), limit);
+        const float u = fminf(fmaxf(to_f32(src[ff + i]), -limit), limit);
+        dst[i] = from_f32<TO>(w * (g / (1.0f + expf(-alpha * g))) * (u + 1.0f));
+    }
+}
+
+// out[t] = sum over k (ascending) of rows[slot[t, k]] (+ shared[t]); rows and shared float32 or bf16, out float32
+template <typename TR>
+__global__ void moe_combine_kernel(const TR* __restrict__ rows, const int* __restrict__ slot, int top, const TR* __restrict__ shared, float* __restrict__ out, int len)
+{
+    pdl_enter();
+    const long long t = blockIdx.x;
+    for (int i = threadIdx.x; i < len; i += blockDim.x) {
+        float acc = 0.f;
+        for (int k = 0; k < top; ++k) acc += to_f32(rows[(long long)slot[t * top + k] * len + i]);
+        if (shared != nullptr) acc += to_f32(shared[t * len + i]);
+        out[t * len + i] = acc;
+    }
+}
+
+extern "C" int spy_moe_route(const float* logits, long long logits_ld, int tokens, int experts, int top, int has_shared, int* choice, float* choice_w,
+                             float* shared_w, int* counts, int* offsets, int* slot, int* row_token, float* row_w, cudaStream_t stream)
+{
+    if (tokens <= 0) return 0;
+    if (experts <= 0 || experts > MOE_MAX_EXPERTS || top <= 0 || top > experts) SPY_FAIL("moe_route: %d experts (at most %d), top %d", experts, MOE_MAX_EXPERTS, top);
+    SPY_CUDA(cudaMemsetAsync(counts, 0, sizeof(int) * experts, stream));
+    const int warps = 4;
+    const int blocks = min((tokens + warps - 1) / warps, 4 * 148);
+    spy_launch_in_order(moe_route_kernel, dim3(blocks), dim3(32 * warps), ((size_t)warps * experts + experts) * sizeof(float), stream, logits, logits_ld,
+                        tokens, experts, top, has_shared, choice, choice_w, shared_w, counts);
+    SPY_CHECK_LAUNCH("moe_route");
+    spy_launch(moe_slots_kernel, dim3(experts), dim3(1024), 0, stream, (const int*)choice, (const float*)choice_w, (const int*)counts,
+               tokens * top, top, experts, offsets, slot, row_token, row_w);
+    SPY_CHECK_LAUNCH("moe_slots");
+    return 0;
+}
+
+extern "C" int spy_gather_rows(const void* in, const int* row_token, void* out, int rows, long long row_bytes, cudaStream_t stream)
+{
+    if (rows <= 0 || row_bytes <= 0) return 0;
+    spy_launch(gather_rows_kernel, dim3(rows), dim3(128), 0, stream, (const uint8_t*)in, row_token, (uint8_t*)out, row_bytes);
+    SPY_CHECK_LAUNCH("gather_rows");
+    return 0;
+}
+
+extern "C" int spy_expert_activation(const void* gu, int gu_dtype, long long gu_ld, const float* row_w, void* y, int y_dtype, long long y_ld, int rows, int ff,
+                                     float limit, float alpha, cudaStream_t stream)
+{
+    if (rows <= 0 || ff <= 0) return 0;
+    const int vec = gu_dtype == SPY_BF16 && y_dtype == SPY_BF16 && ff % 8 == 0 && gu_ld % 8 == 0 && y_ld % 8 == 0
+                    && ((reinterpret_cast<uintptr_t>(gu) | reinterpret_cast<uintptr_t>(y)) & 15) == 0;
+    SPY_DISPATCH_DTYPE(gu_dtype, TA, {
+        SPY_DISPATCH_DTYPE(y_dtype, TO, {
+            spy_launch(expert_activation_kernel<TA, TO>, dim3(rows), dim3(256), 0, stream, (const TA*)gu, gu_ld, row_w, (TO*)y, y_ld, ff, limit, alpha, vec);
+        })
+    })
+    SPY_CHECK_LAUNCH("expert_activation");
+    return 0;
+}
+
+extern "C" int spy_moe_combine(const void* rows, int rows_dtype, const int* slot, int top, const void* shared, float* out, int tokens, int len, cudaStream_t stream)
+{
+    if (tokens <= 0 || len <= 0) return 0;
+    SPY_DISPATCH_DTYPE(rows_dtype, TR, {
+        spy_launch(moe_combine_kernel<TR>, dim3(tokens), dim3(256), 0, stream, (const TR*)rows, slot, top, (const TR*)shared, out, len);
+    })
+    SPY_CHECK_LAUNCH("moe_combine");
+    return 0;
+}

@@ -51,6 +51,18 @@ def _check(t: torch.Tensor, what: str, dtype=None, ndim=None) -> None:
         raise KernelError(f"{what}: expected a contiguous tensor, found strides {t.stride()} for shape {tuple(t.shape)}")
 
 
+def _check_weight(w: torch.Tensor, what: str, dtype=None) -> int:
+    """A weight ``[N, K]`` whose rows are contiguous; the rows themselves may lie apart (a view of some columns of a wider
+    matrix).  Returns the distance between rows in elements."""
+    if not isinstance(w, torch.Tensor) or not w.is_cuda or w.dim() != 2:
+        raise KernelError(f"{what}: expected a CUDA matrix")
+    if dtype is not None and w.dtype != dtype:
+        raise KernelError(f"{what}: expected {dtype}, found {w.dtype}")
+    if w.shape[1] > 1 and w.stride(1) != 1:
+        raise KernelError(f"{what}: rows must be contiguous, found strides {w.stride()}")
+    return int(w.stride(0)) if w.shape[0] > 1 else max(int(w.stride(0)), int(w.shape[1]))
+
+
 def _ptr(t: Optional[torch.Tensor]):
     return ctypes.c_void_p(0 if t is None else t.data_ptr())
 
@@ -696,14 +708,14 @@ def attention_decode(q: torch.Tensor, num_heads: int, head_dim: int, out: torch.
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """``out[M, N] = a[M, K] @ w[N, K]^T`` on the CUDA cores in 32-bit, any sizes and dtypes."""
     _check(a, "gemm input", ndim=2)
-    _check(w, "gemm weight", ndim=2)
+    ldw = _check_weight(w, "gemm weight")
     _check(out, "gemm output", ndim=2)
     M, K = a.shape
     N = w.shape[0]
     if w.shape[1] != K or tuple(out.shape) != (M, N):
         raise KernelError(f"gemm: shapes do not fit: input {tuple(a.shape)}, weight {tuple(w.shape)}, output {tuple(out.shape)}")
     _call("gemm_simt", "spy_gemm_simt", _ptr(a), _code(a, "gemm input"), ctypes.c_longlong(K), _ptr(w), _code(w, "gemm weight"),
-          ctypes.c_longlong(K), _ptr(out), _code(out, "gemm output"), ctypes.c_longlong(N), M, N, K, _stream())
+          ctypes.c_longlong(ldw), _ptr(out), _code(out, "gemm output"), ctypes.c_longlong(N), M, N, K, _stream())
     return out
 
 
@@ -932,9 +944,11 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] =
     rows in ``a`` the blocks ask for its first ``prefetch_bytes`` bytes (0: all) to be brought into L2
     once their own loads are on their way."""
     _check(a, "gemm input", torch.bfloat16, 2)
-    _check(w, "gemm weight", torch.bfloat16, 2)
+    ldw = _check_weight(w, "gemm weight", torch.bfloat16)
     M, K = a.shape
     N = w.shape[0]
+    if ldw % 8 != 0 or w.data_ptr() % 16 != 0:
+        raise KernelError(f"gemm: the weight's rows must start on 16-byte borders (row distance {ldw}, address {w.data_ptr():#x})")
     if w.shape[1] != K:
         raise KernelError(f"gemm: shapes do not fit: input {tuple(a.shape)}, weight {tuple(w.shape)}")
     if epilogue not in (None, "swiglu", "relu2", "geglu_tanh"):
@@ -955,7 +969,7 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] =
         if splits.value > 1:
             stack = torch.empty((splits.value, M, N), dtype=torch.float32, device=a.device)
             used = ctypes.c_int(0)
-            _call("gemm_tcgen05", "spy_gemm_tcgen05_ex", _ptr(a), ctypes.c_longlong(K), _ptr(w), ctypes.c_longlong(K), None, BF16,
+            _call("gemm_tcgen05", "spy_gemm_tcgen05_ex", _ptr(a), ctypes.c_longlong(K), _ptr(w), ctypes.c_longlong(ldw), None, BF16,
                   ctypes.c_longlong(N), M, N, K, _ptr(stack), ctypes.c_longlong(stack.numel()), 0, 1, ctypes.byref(used), _ptr(status),
                   _stream(), pf_ptr, ctypes.c_longlong(pf_bytes))
             if used.value != splits.value:
@@ -968,7 +982,7 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] =
         if tuple(out.shape) != (M, n_out):
             raise KernelError(f"gemm: output {tuple(out.shape)} does not fit [{M}, {n_out}]")
     scratch = _scratch(a.device)
-    _call("gemm_tcgen05", "spy_gemm_tcgen05_ex", _ptr(a), ctypes.c_longlong(K), _ptr(w), ctypes.c_longlong(K), _ptr(out),
+    _call("gemm_tcgen05", "spy_gemm_tcgen05_ex", _ptr(a), ctypes.c_longlong(K), _ptr(w), ctypes.c_longlong(ldw), _ptr(out),
           _code(out, "gemm output"), ctypes.c_longlong(n_out), M, N, K, _ptr(scratch), ctypes.c_longlong(scratch.numel()),
           {None: 0, "swiglu": 1, "relu2": 2, "geglu_tanh": 3}[epilogue], 0, None, _ptr(status), _stream(), pf_ptr, ctypes.c_longlong(pf_bytes))
     return out
@@ -1251,3 +1265,64 @@ def stream_add(stream: torch.Tensor, table: Optional[torch.Tensor], ids: Optiona
     _call("embedding", "spy_stream_add", _ptr(stream), _ptr(table), _code(table, "embedding table") if table is not None else 0, _ptr(ids), _ptr(row),
           _code(row, "offset row") if row is not None else 0, T, H, V, _ptr(status), _stream())
     return stream
+
+
+def moe_route(logits: torch.Tensor, experts: int, top: int, has_shared: bool):
+    """Sorts the (token, chosen expert) pairs of a step by expert.  ``logits [T, >= experts (+ 1)]`` float32 as for
+    ``moe_activation``.  Returns ``offsets [experts + 1]`` (where each expert's run of rows starts), ``slot [T, top]`` (the row
+    of each pair, the chosen experts in ascending order), ``row_token [T top]``, ``row_w [T top]`` (each row's token and its
+    softmax score over all experts) and ``shared_w [T]`` (sigmoid of the shared gate's logit) or None."""
+    _check(logits, "router logits", torch.float32, 2)
+    T = logits.shape[0]
+    if logits.shape[1] < experts + (1 if has_shared else 0):
+        raise KernelError("moe_route: the logits lack columns")
+    dev = logits.device
+    ints = torch.empty((2 * T * top + T * top + experts + experts + 1,), dtype=torch.int32, device=dev)
+    choice, slot, row_token = ints[:T * top], ints[T * top:2 * T * top], ints[2 * T * top:3 * T * top]
+    counts, offsets = ints[3 * T * top:3 * T * top + experts], ints[3 * T * top + experts:]
+    floats = torch.empty((2 * T * top + T,), dtype=torch.float32, device=dev)
+    choice_w, row_w, shared_w = floats[:T * top], floats[T * top:2 * T * top], floats[2 * T * top:]
+    _call("moe", "spy_moe_route", _ptr(logits), ctypes.c_longlong(logits.shape[1]), T, int(experts), int(top), int(bool(has_shared)), _ptr(choice),
+          _ptr(choice_w), _ptr(shared_w), _ptr(counts), _ptr(offsets), _ptr(slot), _ptr(row_token), _ptr(row_w), _stream())
+    return offsets, slot.view(T, top), row_token, row_w, (shared_w if has_shared else None)
+
+
+def gather_rows(x: torch.Tensor, row_token: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """``out[r] = x[row_token[r]]``."""
+    _check(x, "gathered tensor", ndim=2)
+    _check(out, "gather output", x.dtype, 2)
+    _check(row_token, "row tokens", torch.int32, 1)
+    if out.shape[1] != x.shape[1] or out.shape[0] != row_token.shape[0]:
+        raise KernelError("gather_rows: shapes do not fit")
+    _call("moe", "spy_gather_rows", _ptr(x), _ptr(row_token), _ptr(out), out.shape[0], ctypes.c_longlong(x.shape[1] * x.element_size()), _stream())
+    return out
+
+
+def expert_activation(gate_up: torch.Tensor, row_w: torch.Tensor, out: torch.Tensor, limit: float, alpha: float = 1.702) -> torch.Tensor:
+    """``out[r] = row_w[r] * g * sigmoid(alpha g) * (u + 1)`` over rows ``[gate | up]`` with ``g = min(gate, limit)``, ``u = clamp(up, -limit, limit)``."""
+    _check(gate_up, "expert gate|up", ndim=2)
+    _check(out, "expert activations", ndim=2)
+    _check(row_w, "row weights", torch.float32, 1)
+    R, two = gate_up.shape
+    if two % 2 or tuple(out.shape) != (R, two // 2) or row_w.shape[0] < R:
+        raise KernelError("expert_activation: shapes do not fit")
+    _call("moe", "spy_expert_activation", _ptr(gate_up), _code(gate_up, "expert gate|up"), ctypes.c_longlong(two), _ptr(row_w), _ptr(out),
+          _code(out, "expert activations"), ctypes.c_longlong(two // 2), R, two // 2, ctypes.c_float(limit), ctypes.c_float(alpha), _stream())
+    return out
+
+
+def moe_combine(rows: torch.Tensor, slot: torch.Tensor, shared: Optional[torch.Tensor], out: torch.Tensor) -> torch.Tensor:
+    """``out[t] = sum_k rows[slot[t, k]] (+ shared[t])`` in 32-bit, the sum in the order of ``k``."""
+    _check(rows, "expert results", ndim=2)
+    _check(slot, "slots", torch.int32, 2)
+    _check(out, "mixture output", torch.float32, 2)
+    T, top = slot.shape
+    if tuple(out.shape) != (T, rows.shape[1]) or rows.shape[0] != T * top:
+        raise KernelError("moe_combine: shapes do not fit")
+    if shared is not None:
+        _check(shared, "shared expert result", rows.dtype, 2)
+        if tuple(shared.shape) != tuple(out.shape):
+            raise KernelError("moe_combine: the shared expert's result does not fit")
+    _call("moe", "spy_moe_combine", _ptr(rows), _code(rows, "expert results"), _ptr(slot), top, _ptr(shared), _ptr(out), T, rows.shape[1], _stream())
+    return out
+

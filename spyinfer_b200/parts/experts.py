@@ -8,8 +8,18 @@ own) runs for every token, weighted by ``sigmoid(W_sg h)``, one number a token.
 All experts' gate and up projections are one product, their down projections one product over the activations side by
 side; the kernel between the two multiplies each expert's activation by the token's weight for it, which is exactly zero
 for an expert that the token did not choose.  A token's result therefore does not depend on what else is in the batch.
+
+A step of many tokens (``routed_from`` or more: by default so many that an expert gets 1,024 rows on average, below which its
+products fill too little of the GPU to gain; ``SPYINFER_MOE_ROUTED_FROM`` in the environment sets the number, 0 turns the form
+off; never inside a captured graph) takes the routed form instead: the (token, chosen expert) pairs are sorted by expert on the
+device, the tokens' rows gathered in that order, each expert's two products run on its own run of rows (views of the same
+fused weights, nothing stored twice), and every token's ``top`` results and the shared expert's are added in a fixed order in
+32-bit.  The experts' row counts are read back once a layer to size the products.  Weights and arithmetic are the same, so the
+two forms differ by the order of sums only.
 """
 from __future__ import annotations
+
+import os
 
 import torch
 
@@ -39,6 +49,11 @@ class ExpertMixture(FeedForward):
         self.prefix = params.get("prefix", "")
         self.cols = self.experts * self.ff + self.shared_ff
         self.router = self.gate_up = self.down = None
+        default = -(-1024 * self.experts // self.top)
+        try:
+            self.routed_from = int(os.environ.get("SPYINFER_MOE_ROUTED_FROM", params.get("routed_from", default)))
+        except ValueError:
+            self.routed_from = default
 
     def weight_decls(self):
         p, W = self.prefix, self.hidden
@@ -70,8 +85,35 @@ class ExpertMixture(FeedForward):
         return [self.router, self.gate_up, self.down]
 
     def forward(self, x):
+        if 0 < self.routed_from <= x.shape[0] and self.top < self.experts and not torch.cuda.is_current_stream_capturing():
+            return self._routed(x)
         logits = self.router(x, out_dtype=torch.float32)
         gu = self.gate_up(x)
         y = torch.empty((x.shape[0], self.cols), dtype=self.ctx.dtype, device=x.device)
         kernels.moe_activation(gu, logits, y, self.experts, self.top, self.ff, self.limit, self.shared_ff, self.shared_limit, self.slope)
         return self.down(y, defer=self.defer_output)
+
+    def _routed(self, x):
+        T, E, top, ff, sff, dev = x.shape[0], self.experts, self.top, self.ff, self.shared_ff, x.device
+        logits = self.router(x, out_dtype=torch.float32)
+        offsets, slot, row_token, row_w, shared_w = kernels.moe_route(logits, E, top, bool(sff))
+        starts = offsets.cpu().tolist()                      # the layer's one read-back: the experts' row counts size their products
+        R = T * top
+        rows = kernels.gather_rows(x, row_token, torch.empty((R, self.hidden), dtype=x.dtype, device=dev))
+        gu = torch.empty((R, 2 * ff), dtype=self.ctx.dtype, device=dev)
+        for e in range(E):
+            a, b = starts[e], starts[e + 1]
+            if b > a:
+                self.gate_up.part(rows[a:b], rows=(2 * ff * e, 2 * ff * (e + 1)), out=gu[a:b])
+        y = kernels.expert_activation(gu, row_w, torch.empty((R, ff), dtype=self.ctx.dtype, device=dev), self.limit, self.slope)
+        results = torch.empty((R, self.hidden), dtype=torch.float32, device=dev)
+        for e in range(E):
+            a, b = starts[e], starts[e + 1]
+            if b > a:
+                self.down.part(y[a:b], cols=(ff * e, ff * (e + 1)), out=results[a:b])
+        shared = None
+        if sff:
+            sgu = self.gate_up.part(x, rows=(2 * ff * E, 2 * ff * E + 2 * sff), out_dtype=self.ctx.dtype)
+            sy = kernels.expert_activation(sgu, shared_w, torch.empty((T, sff), dtype=self.ctx.dtype, device=dev), self.shared_limit, self.slope)
+            shared = self.down.part(sy, cols=(ff * E, ff * E + sff), out_dtype=torch.float32)
+        return kernels.moe_combine(results, slot, shared, torch.empty((T, self.hidden), dtype=torch.float32, device=dev))

@@ -70,3 +70,18 @@ class Linear:
             raise ValueError("only the tensor-core product has fused epilogues")
         out = torch.empty((x.shape[0], self.out_features), dtype=out_dtype or x.dtype, device=x.device)
         return kernels.gemm_simt(x, self.weight, out)
+
+    def part(self, x: torch.Tensor, rows=None, cols=None, out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        """The product with a part of the weight: ``rows = (first, end)`` of its output rows and/or ``cols = (first, end)`` of its
+        inputs (``x`` then has ``end - first`` columns).  The part is a view; nothing is copied.  No bias, no epilogue."""
+        w = self.weight
+        if rows is not None:
+            w = w[rows[0]:rows[1]]
+        if cols is not None:
+            w = w[:, cols[0]:cols[1]]
+        if out is None:
+            out = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype or x.dtype, device=x.device)
+        if self.fast and w.shape[1] % 8 == 0 and w.data_ptr() % 16 == 0:
+            return kernels.gemm_tcgen05(x, w, out=out)
+        return kernels.gemm_simt(x, w, out)
+

@@ -820,3 +820,65 @@ def test_greedy_generation_through_the_engine_and_its_scheduler(models, name):
             toks.append(int(logits.argmax()))
             assert out[i] == toks[-1], (i, out, toks[len(prompt):])
     assert engine.stats()["free_slots"] == 3
+
+
+# ---- the routed form of the expert mixture ----------------------------------------------------------------
+
+@gpu
+@pytest.mark.parametrize("experts,top,shared", [(6, 2, True), (5, 1, False), (16, 4, True), (64, 6, False), (3, 2, True)])
+def test_pairs_of_token_and_expert_sorted_by_expert(experts, top, shared):
+    from spyinfer_b200 import kernels
+
+    g = torch.Generator().manual_seed(experts + top)
+    T = 75
+    logits = torch.randn(T, experts + (1 if shared else 0), generator=g) * 2
+    scores = torch.softmax(logits[:, :experts].double(), -1)
+    best = torch.topk(scores, top, dim=-1).indices.sort(dim=-1).values                # the chosen experts in ascending order
+    offsets, slot, row_token, row_w, shared_w = kernels.moe_route(logits.cuda(), experts, top, shared)
+    offsets, slot, row_token, row_w = offsets.cpu(), slot.cpu(), row_token.cpu(), row_w.cpu()
+    counts = torch.bincount(best.flatten(), minlength=experts)
+    assert offsets.tolist() == [0] + counts.cumsum(0).tolist()
+    assert sorted(slot.flatten().tolist()) == list(range(T * top))                    # every row is used once
+    for t in range(T):
+        for k in range(top):
+            r, e = int(slot[t, k]), int(best[t, k])
+            assert offsets[e] <= r < offsets[e + 1] and int(row_token[r]) == t
+            assert abs(float(row_w[r]) - float(scores[t, e])) < 1e-6
+    for e in range(experts):                                                          # within an expert's run the tokens keep their order
+        run = row_token[int(offsets[e]):int(offsets[e + 1])].tolist()
+        assert run == sorted(run)
+    if shared:
+        assert torch.allclose(shared_w.cpu().double(), torch.sigmoid(logits[:, experts].double()), atol=1e-6)
+    # gathered rows, activations with a weight a row, and the sum of each token's results
+    x = torch.randn(T, 24, generator=g).to(torch.bfloat16)
+    rows = kernels.gather_rows(x.cuda(), row_token.cuda(), torch.empty((T * top, 24), dtype=torch.bfloat16, device="cuda"))
+    assert torch.equal(rows.cpu(), x[row_token.long()])
+    gu = torch.randn(T * top, 2 * 10, generator=g) * 2
+    y = kernels.expert_activation(gu.cuda(), row_w.cuda(), torch.empty((T * top, 10), dtype=torch.float32, device="cuda"), 1.3)
+    ga, up = torch.clamp(gu[:, :10].double(), max=1.3), torch.clamp(gu[:, 10:].double(), -1.3, 1.3)
+    assert torch.allclose(y.cpu().double(), row_w.double()[:, None] * ga * torch.sigmoid(1.702 * ga) * (up + 1), atol=1e-5)
+    res, sh = torch.randn(T * top, 12, generator=g), torch.randn(T, 12, generator=g)
+    out = kernels.moe_combine(res.cuda(), slot.cuda(), sh.cuda(), torch.empty((T, 12), dtype=torch.float32, device="cuda"))
+    assert torch.allclose(out.cpu(), res[slot.long()].sum(1) + sh, atol=1e-5)
+
+
+@gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["a", "b", "c", "d"])
+def test_the_routed_mixture_agrees_with_the_plain_model_and_with_the_dense_form(models, name, dtype, monkeypatch):
+    """Steps of eight tokens or more take the routed form (each expert's products on its own rows), shorter ones and decoding the
+    dense one; both agree with the plain model, and in float32 with each other to rounding."""
+    toks = tokens_of(name, 150, salt=8)
+    want = plain_logits(name, models, toks)
+    dense = run_cuts(make_runner(models[name][0], dtype), "w", toks, [150])
+    monkeypatch.setenv("SPYINFER_MOE_ROUTED_FROM", "8")
+    runner = make_runner(models[name][0], dtype)
+    mixtures = [l.feed_forward for l in runner.model.layers if getattr(l.feed_forward, "routed_from", None) is not None]
+    assert mixtures and all(m.routed_from == 8 for m in mixtures)
+    whole = run_cuts(runner, "w", toks, [150])
+    agrees(whole, want, dtype, "routed, whole")
+    portions = run_cuts(runner, "p", toks, cycle_cuts(150, [2, 31, 8, 3, 64, 9]))
+    agrees(portions, want, dtype, "routed and dense portions")
+    if dtype == "float32":
+        scale = np.abs(dense).max()
+        assert np.abs(whole - dense).max() / scale < 4e-6 and np.abs(portions - dense).max() / scale < 4e-6
