@@ -31,7 +31,7 @@ from typing import Dict, Hashable, List, Optional, Sequence
 import numpy as np
 import torch
 
-from ..config.spec import CompositeCacheNeed, PagedCacheNeed, StateCacheNeed
+from ..config.spec import CompositeCacheNeed, PagedCacheNeed, SharedCacheNeed, StateCacheNeed
 from . import core
 from .core import NoFreeSlot, OutOfPages
 
@@ -106,6 +106,13 @@ class CacheManager:
         def make(i: int, need) -> CacheView:
             if need is None:
                 return CacheView(kind="none")
+            if isinstance(need, SharedCacheNeed):
+                if cache_of[i] is None:
+                    raise ValueError(f"run-order entry {i}: a part of its need is another entry's cache, and it names none")
+                theirs = self._views[cache_of[i]].paged_views()
+                if len(theirs) != 1:
+                    raise ValueError(f"run-order entry {i}: entry {cache_of[i]} has {len(theirs)} paged caches, exactly one can be read from outside")
+                return shared(theirs[0])
             if isinstance(need, CompositeCacheNeed):
                 return CacheView(kind="composite", parts=[make(i, p) for p in need.parts])
             if isinstance(need, PagedCacheNeed):
@@ -129,16 +136,23 @@ class CacheManager:
             raise TypeError(f"run-order entry {i}: unknown cache need {need!r}")
 
         for i, need in enumerate(needs):
-            self._views.append(shared(self._views[cache_of[i]]) if cache_of[i] is not None else make(i, need))
+            # an entry that reads another's cache keeps nothing of its own, unless its need has a part marked ``SharedCacheNeed``:
+            # then that part is the other entry's pages, and the entry keeps the other parts itself
+            flat = need.flat() if isinstance(need, CompositeCacheNeed) else [need]
+            reads_whole = cache_of[i] is not None and not any(isinstance(n, SharedCacheNeed) for n in flat)
+            self._views.append(shared(self._views[cache_of[i]]) if reads_whole else make(i, need))
         # the bookkeeping (pools, block tables, slots, requests) lives in the C++ engine core
         self._lib = core.lib()
         windows = (ctypes.c_int * max(1, len(self.groups)))(*[(-1 if g.need.window is None else int(g.need.window)) for g in self.groups])
-        self.group_pages = [self.pages_of_group(g.need.window, page_size, num_pages, max_num_seqs, max_step_tokens, g.need.stride) for g in self.groups]
+        self.group_pages = [self.pages_of_group(g.need.window, page_size, num_pages, max_num_seqs, max_step_tokens, g.need.stride, g.need.keep_first) for g in self.groups]
         sizes = (ctypes.c_int * max(1, len(self.groups)))(*self.group_pages)
         strides = (ctypes.c_int * max(1, len(self.groups)))(*[int(g.need.stride) for g in self.groups])
         self._h = self._lib.spy_cache_create(len(self.groups), windows, sizes, strides, page_size, num_pages, max_num_seqs, max_model_len)
         if not self._h:
             raise ValueError(core.build.last_error("engine_core"))
+        for gi, g in enumerate(self.groups):
+            if g.need.window is not None and g.need.keep_first and self._lib.spy_cache_keep_first(self._h, gi, int(g.need.keep_first)) != 0:
+                raise ValueError(core.build.last_error("engine_core"))
         for gi, g in enumerate(self.groups):
             g.tables = np.ctypeslib.as_array(self._lib.spy_cache_tables(self._h, gi), shape=(max_num_seqs, self.width))
         if device is not None:
@@ -180,15 +194,17 @@ class CacheManager:
 
     # ---- sizes -------------------------------------------------------------------------
     @staticmethod
-    def pages_of_group(window: Optional[int], page_size: int, num_pages: int, max_num_seqs: int, max_step_tokens: Optional[int], stride: int = 1) -> int:
+    def pages_of_group(window: Optional[int], page_size: int, num_pages: int, max_num_seqs: int, max_step_tokens: Optional[int], stride: int = 1,
+                       keep_first: int = 0) -> int:
         """The pool size of a group with this window (None: every key is kept) and stride (an entry for
         every so many tokens: the requests of a full pool of ``num_pages`` then hold a ``stride``-th of
-        that many entries, and each of them may leave one page partly filled)."""
+        that many entries, and each of them may leave one page partly filled).  A windowed group that keeps
+        a sequence's first ``keep_first`` positions holds their pages beside the window's."""
         if stride > 1:
             return max(1, min(num_pages, (num_pages + stride - 1) // stride + max_num_seqs))
         if window is None or max_step_tokens is None:
             return num_pages
-        per_request = (int(window) + int(max_step_tokens) + page_size - 1) // page_size + 2
+        per_request = (int(window) + int(max_step_tokens) + page_size - 1) // page_size + 2 + (int(keep_first) + page_size - 1) // page_size
         return max(1, min(num_pages, max_num_seqs * per_request))
 
     @staticmethod

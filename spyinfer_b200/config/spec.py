@@ -123,7 +123,9 @@ class PagedCacheNeed:
     summary of each block of that many tokens, stored when the block's last token is), so a
     request of ``L`` tokens holds ``L // stride`` entries; such a need has no window.  ``planes``
     is 2 for keys and values, 1 for a mixer whose values are its keys (or a part of them, as a
-    latent that keys and values are both projected from): a page then holds keys only.  Entries of
+    latent that keys and values are both projected from): a page then holds keys only.
+    ``keep_first`` (with a window): the entries of a sequence's first so many positions stay
+    visible to every later query, so the pages that hold them are never given back.  Entries of
     the run order with equal needs share one group of pages in the cache manager.
     """
 
@@ -132,15 +134,18 @@ class PagedCacheNeed:
     window: Optional[int] = None
     stride: int = 1
     planes: int = 2
+    keep_first: int = 0
 
     def __post_init__(self):
         if self.planes not in (1, 2):
             raise ValueError(f"a paged need has 1 or 2 planes, found {self.planes}")
+        if self.keep_first < 0:
+            raise ValueError(f"a paged need keeps the first {self.keep_first} positions: not negative")
         if self.stride < 1 or (self.stride > 1 and self.window is not None):
             raise ValueError(f"a paged need's stride must be at least 1, and with a stride above 1 there is no window (found stride {self.stride}, window {self.window})")
 
     def group_key(self) -> Tuple:
-        return ("paged", self.num_kv_heads, self.head_dim, self.window, self.stride, self.planes)
+        return ("paged", self.num_kv_heads, self.head_dim, self.window, self.stride, self.planes, self.keep_first if self.window is not None else 0)
 
 
 @dataclass(frozen=True)
@@ -152,6 +157,16 @@ class StateCacheNeed:
 
     def group_key(self) -> Tuple:
         return ("state", tuple(self.shape), self.dtype)
+
+
+@dataclass(frozen=True)
+class SharedCacheNeed:
+    """Inside the need of a run-order entry that names another entry in ``cache_of``: this part is that entry's paged
+    cache (its only one), read and never written.  It lets an entry read another's keys and values and still keep
+    things of its own beside them (the state of an input convolution, say)."""
+
+    def group_key(self) -> Tuple:
+        return ("shared",)
 
 
 @dataclass(frozen=True)

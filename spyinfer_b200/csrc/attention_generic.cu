@@ -12,6 +12,9 @@
 // o = sum p v.  Formula: spymaster2h/spyinfer src/backends/cpu/cpu_attention.cpp:89-135.
 // Keys are processed in chunks of 128 that start at multiples of 128 of the absolute
 // position, so the result of a query does not depend on how the batch was cut.
+// Two options of the mask and the softmax: with a window, `keep_first` > 0 lets every query also see
+// the keys at the sequence's first keep_first positions (at their true positions); `sink` != 0 adds one
+// to the softmax's denominator (a key of score 0 that has no value): p = exp(score) / (1 + sum exp(score)).
 #include "common.cuh"
 
 SPY_MODULE(spy_attention_generic)
@@ -41,7 +44,8 @@ template <typename TA, typename TC>
 __global__ void __launch_bounds__(CHUNK)
 attention_generic_kernel(const TA* __restrict__ q, long long q_row_stride, TA* __restrict__ out, const TC* __restrict__ pages,
                          const int* __restrict__ block_table, int table_width, int page_size, int num_pages, int nh, int nkv, int hd,
-                         const int* __restrict__ positions, const int* __restrict__ seq_of_token, int window, float scale, int* status, int planes)
+                         const int* __restrict__ positions, const int* __restrict__ seq_of_token, int window, float scale, int* status, int planes,
+                         int keep_first, int sink)
 {
     extern __shared__ float smem[];
     pdl_enter();
@@ -68,9 +72,15 @@ attention_generic_kernel(const TA* __restrict__ q, long long q_row_stride, TA* _
     for (int r = 0; r < ACC; ++r) acc[r] = 0.f;
     __syncthreads();
 
-    for (int c = lo / CHUNK; c <= pos / CHUNK; ++c) {
+    const int kept = min(keep_first, lo);             // the keys 0 .. kept - 1 lie before the window and are seen all the same
+    const int kept_chunks = (kept + CHUNK - 1) / CHUNK;
+    for (int c = 0; c <= pos / CHUNK; ++c) {
+        if (c >= kept_chunks && c < lo / CHUNK) {
+            c = lo / CHUNK - 1;                       // nothing to see between the kept keys and the window
+            continue;
+        }
         const int j = c * CHUNK + tid;
-        bool valid = j >= lo && j <= pos;
+        bool valid = (j >= lo || j < kept) && j <= pos;
         long long row = 0;
         if (valid) {
             const int lp = j / page_size;
@@ -110,18 +120,23 @@ attention_generic_kernel(const TA* __restrict__ q, long long q_row_stride, TA* _
         const float chunk_sum = block_sum(p, scratch);  // its barriers also publish p_s and row_s
         l = l * alpha + chunk_sum;
         m = m_new;
-        const int first = max(lo, c * CHUNK) - c * CHUNK, last = min(pos, c * CHUNK + CHUNK - 1) - c * CHUNK;
+        const int first = (c < kept_chunks ? 0 : max(lo, c * CHUNK) - c * CHUNK), last = min(pos, c * CHUNK + CHUNK - 1) - c * CHUNK;
+        const int gap_first = c < kept_chunks ? kept - c * CHUNK : CHUNK, gap_end = c < kept_chunks ? lo - c * CHUNK : 0;   // [gap_first, gap_end): unseen keys inside the chunk
 #pragma unroll
         for (int r = 0; r < ACC; ++r) {
             const int d = tid + r * CHUNK;
             if (d < hd) {
                 float a = acc[r] * alpha;
-                for (int jj = first; jj <= last; ++jj) a = fmaf(p_s[jj], to_f32(pages[row_s[jj] + v_offset + d]), a);
+                for (int jj = first; jj <= last; ++jj) {
+                    if (jj >= gap_first && jj < gap_end) continue;
+                    a = fmaf(p_s[jj], to_f32(pages[row_s[jj] + v_offset + d]), a);
+                }
                 acc[r] = a;
             }
         }
         __syncthreads();  // p_s and row_s are rewritten by the next chunk
     }
+    if (sink) l += m == -INFINITY ? 1.f : expf(-m);      // the key of score 0 without a value
     TA* o_row = out + ((size_t)t * nh + h) * hd;
 #pragma unroll
     for (int r = 0; r < ACC; ++r) {
@@ -135,8 +150,9 @@ attention_generic_kernel(const TA* __restrict__ q, long long q_row_stride, TA* _
 extern "C" int spy_attention_generic(const void* q, long long q_row_stride, void* out, int act_dtype, const void* pages, int cache_dtype,
                                      const int* block_table, int table_width, int page_size, int num_pages, int nh, int nkv, int hd,
                                      const int* positions, const int* seq_of_token, int tokens, int window, float scale, int* status,
-                                     cudaStream_t stream, int planes)
+                                     cudaStream_t stream, int planes, int keep_first, int sink)
 {
+    if (keep_first < 0 || (keep_first > 0 && window <= 0)) SPY_FAIL("attention: kept first keys (%d) go with a window", keep_first);
     if (tokens <= 0) return 0;
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0) SPY_FAIL("attention: %d query heads do not group over %d key/value heads", nh, nkv);
     if (hd <= 0 || hd > ACC * CHUNK) SPY_FAIL("attention: head_dim %d must be positive and at most %d", hd, ACC * CHUNK);
@@ -149,7 +165,7 @@ extern "C" int spy_attention_generic(const void* q, long long q_row_stride, void
         SPY_DISPATCH_DTYPE(cache_dtype, TC, {
             spy_launch(attention_generic_kernel<TA, TC>, grid, dim3(CHUNK), smem, stream,
                 (const TA*)q, q_row_stride, (TA*)out, (const TC*)pages, block_table, table_width, page_size, num_pages, nh, nkv, hd,
-                positions, seq_of_token, window, scale, status, planes);
+                positions, seq_of_token, window, scale, status, planes, keep_first, sink);
         })
     })
     SPY_CHECK_LAUNCH("attention_generic");

@@ -66,6 +66,7 @@ struct PagePool {
 
 struct Group {
     int window;                    // -1: every key is kept
+    int keep_first = 0;            // with a window: the pages of a request's first so many positions are never given back
     int stride;                    // one entry of the group for every `stride` tokens of a request (1: an entry a token);
                                    // an entry exists once all its tokens do, so a request of L tokens holds L / stride entries
     PagePool pool;
@@ -237,6 +238,15 @@ void* spy_cache_create(int num_groups, const int* windows, const int* group_page
 
 void spy_cache_destroy(void* h) { delete static_cast<Cache*>(h); }
 
+// A windowed group whose queries also see a sequence's first `keep_first` positions: the pages that hold them stay.
+int spy_cache_keep_first(void* h, int group, int keep_first)
+{
+    Cache* c = static_cast<Cache*>(h);
+    if (group < 0 || group >= (int)c->groups.size() || keep_first < 0) return fail(BAD_VALUE, "group %d of %d keeps its first %d positions", group, (int)c->groups.size(), keep_first);
+    c->groups[(size_t)group].keep_first = keep_first;
+    return OK;
+}
+
 int spy_cache_width(void* h) { return static_cast<Cache*>(h)->width; }
 int spy_cache_num_free_pages(void* h, int group)
 {
@@ -310,7 +320,7 @@ int spy_cache_commit(void* h, int64_t rid, int new_length)
         if (g.window < 0) continue;
         const int first_needed = std::max(0, new_length - g.window + 1) / c->page_size;   // lowest page a query at new_length or later still sees
         int32_t* row = g.tables.data() + (size_t)r->slot * c->width;
-        for (int lp = 0; lp < first_needed && lp < c->width; ++lp)
+        for (int lp = c->pages_for(g.keep_first); lp < first_needed && lp < c->width; ++lp)
             if (row[lp] >= 0) {
                 if (int rc = g.pool.release(row[lp])) return rc;
                 row[lp] = -1;

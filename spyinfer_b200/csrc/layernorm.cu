@@ -1,7 +1,8 @@
-// Layer norm with a weight and no bias, optionally fused with a scaled residual sum and a row gather.
-//   v      = x[row] + scale_a * sum_s a[s][row] + scale_b * sum_s b[s][row]          32-bit sums, parts in their order
+// Layer norm with a weight and an optional bias, optionally fused with a scaled residual sum and a row gather.
+//   v      = x[row] + scale_a * a_w * sum_s a[s][row] + scale_b * sum_s b[s][row]    32-bit sums, parts in their order
 //   x[row] = v                                             when write_back (the residual stream)
-//   out    = (v - mean(v)) / sqrt(mean((v - mean(v))^2) + eps) * w                   32-bit statistics, two passes
+//   out    = (v - mean(v)) / sqrt(mean((v - mean(v))^2) + eps) * w (+ bias)          32-bit statistics, two passes
+// a_w (null, or [len] of the weight's type) multiplies the first result element by element along the row (a layer scale).
 // a and b are null, one array [*, len], or stacks of split-K partial products (splits arrays, split_stride elements
 // apart); two of them because a layer whose mixer is two mixers side by side hands over two results with a weight each.
 // With center == 0 the mean is not removed (an RMS norm with the same fused sums).
@@ -40,7 +41,7 @@ template <typename TX, typename TD, typename TW, typename TO, bool VEC>
 __global__ void __launch_bounds__(1024)
 layernorm_kernel(TX* x, const TD* __restrict__ a, int a_splits, long long a_stride, float a_scale, const TD* __restrict__ b, int b_splits,
                  long long b_stride, float b_scale, const int* __restrict__ rows, const TW* __restrict__ w, TO* __restrict__ out, int len, float eps,
-                 int write_back, int center)
+                 int write_back, int center, const TW* __restrict__ bias, const TW* __restrict__ a_w)
 {
     extern __shared__ __align__(16) float row_buf[];  // len floats, then 33 of scratch
     pdl_enter();
@@ -62,6 +63,12 @@ layernorm_kernel(TX* x, const TD* __restrict__ a, int a_splits, long long a_stri
                 if constexpr (VEC) Quad<TD>::load(ar + (size_t)s * a_stride + i, p); else p[0] = to_f32(ar[(size_t)s * a_stride + i]);
 #pragma unroll
                 for (int e = 0; e < E; ++e) d[e] += p[e];
+            }
+            if (a_w) {
+                float aw[4];
+                if constexpr (VEC) Quad<TW>::load(a_w + i, aw); else aw[0] = to_f32(a_w[i]);
+#pragma unroll
+                for (int e = 0; e < E; ++e) d[e] *= aw[e];
             }
 #pragma unroll
             for (int e = 0; e < E; ++e) v[e] = fmaf(a_scale, d[e], v[e]);
@@ -102,15 +109,21 @@ layernorm_kernel(TX* x, const TD* __restrict__ a, int a_splits, long long a_stri
         if constexpr (VEC) Quad<TW>::load(w + i, wv); else wv[0] = to_f32(w[i]);
 #pragma unroll
         for (int e = 0; e < E; ++e) o[e] = ((row_buf[i + e] - mean) * inv) * wv[e];
+        if (bias) {
+            float bv[4];
+            if constexpr (VEC) Quad<TW>::load(bias + i, bv); else bv[0] = to_f32(bias[i]);
+#pragma unroll
+            for (int e = 0; e < E; ++e) o[e] += bv[e];
+        }
         if constexpr (VEC) Quad<TO>::store(orow + i, o); else orow[i] = from_f32<TO>(o[0]);
     }
 }
 
 // x: [*, len] of x_dtype; a, b: null or stacks of delta_dtype; rows: null or n row indices (gather); w: [len] of w_dtype;
-// out: [n, len] of out_dtype.  write_back stores the sum into x and needs rows == null.
-extern "C" int spy_layernorm(void* x, int x_dtype, const void* a, int a_splits, long long a_stride, float a_scale, const void* b, int b_splits,
-                             long long b_stride, float b_scale, int delta_dtype, const int* rows, const void* w, int w_dtype, void* out, int out_dtype,
-                             int n, int len, float eps, int write_back, int center, cudaStream_t stream)
+// out: [n, len] of out_dtype.  write_back stores the sum into x and needs rows == null.  bias, a_w: null or [len] of w_dtype.
+static int run_layernorm(void* x, int x_dtype, const void* a, int a_splits, long long a_stride, float a_scale, const void* b, int b_splits,
+                         long long b_stride, float b_scale, int delta_dtype, const int* rows, const void* w, int w_dtype, void* out, int out_dtype,
+                         int n, int len, float eps, int write_back, int center, const void* bias, const void* a_w, cudaStream_t stream)
 {
     if (n <= 0) return 0;
     if (len <= 0) SPY_FAIL("layernorm: row length %d must be positive", len);
@@ -122,7 +135,7 @@ extern "C" int spy_layernorm(void* x, int x_dtype, const void* a, int a_splits, 
     if (smem > 227 * 1024) SPY_FAIL("layernorm: a row of %d elements does not fit in shared memory (limit %d)", len, (227 * 1024) / 4 - 33);
     const bool vec = len % 4 == 0 && a_stride % 4 == 0 && b_stride % 4 == 0 &&
                      ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(w) |
-                       reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+                       reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(bias) | reinterpret_cast<uintptr_t>(a_w)) & 15) == 0;
     // many rows: fewer threads a row (two quads each) and so more rows an SM at a time; few rows: the row spread as wide as it goes
     int threads = (len / (vec ? (n >= 512 ? 8 : 4) : 4) + 31) / 32 * 32;
     threads = threads < 64 ? 64 : (threads > 1024 ? 1024 : threads);
@@ -133,13 +146,31 @@ extern "C" int spy_layernorm(void* x, int x_dtype, const void* a, int a_splits, 
                     auto kernel = vec ? layernorm_kernel<TX, TD, TW, TO, true> : layernorm_kernel<TX, TD, TW, TO, false>;
                     if (smem > 48 * 1024) SPY_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
                     spy_launch(kernel, dim3(n), dim3(threads), smem, stream, (TX*)x, (const TD*)a, a_splits, a_stride, a_scale, (const TD*)b, b_splits,
-                               b_stride, b_scale, rows, (const TW*)w, (TO*)out, len, eps, write_back, center);
+                               b_stride, b_scale, rows, (const TW*)w, (TO*)out, len, eps, write_back, center, (const TW*)bias, (const TW*)a_w);
                 })
             })
         })
     })
     SPY_CHECK_LAUNCH("layernorm");
     return 0;
+}
+
+extern "C" int spy_layernorm(void* x, int x_dtype, const void* a, int a_splits, long long a_stride, float a_scale, const void* b, int b_splits,
+                             long long b_stride, float b_scale, int delta_dtype, const int* rows, const void* w, int w_dtype, void* out, int out_dtype,
+                             int n, int len, float eps, int write_back, int center, cudaStream_t stream)
+{
+    return run_layernorm(x, x_dtype, a, a_splits, a_stride, a_scale, b, b_splits, b_stride, b_scale, delta_dtype, rows, w, w_dtype, out, out_dtype, n, len,
+                         eps, write_back, center, nullptr, nullptr, stream);
+}
+
+// The same with a bias behind the weight and a per-channel multiplier of the first result (each null or [len] of w_dtype).
+extern "C" int spy_layernorm_affine(void* x, int x_dtype, const void* a, int a_splits, long long a_stride, float a_scale, const void* a_w, const void* b,
+                                    int b_splits, long long b_stride, float b_scale, int delta_dtype, const int* rows, const void* w, const void* bias,
+                                    int w_dtype, void* out, int out_dtype, int n, int len, float eps, int write_back, int center, cudaStream_t stream)
+{
+    if (a_w != nullptr && a == nullptr) SPY_FAIL("layernorm: a per-channel multiplier without a result to multiply");
+    return run_layernorm(x, x_dtype, a, a_splits, a_stride, a_scale, b, b_splits, b_stride, b_scale, delta_dtype, rows, w, w_dtype, out, out_dtype, n, len,
+                         eps, write_back, center, bias, a_w, stream);
 }
 
 // out = scale_a * sum_s a[s] + scale_b * sum_s b[s], element by element in 32-bit: the weighted sum of two results (each

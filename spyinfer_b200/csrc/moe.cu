@@ -7,45 +7,94 @@
 // experts in 32-bit, the `top` largest scores keep their value, the others become 0; ties go to the lower index) and writes
 //     y[t, e, i] = weight[t, e] * g * sigmoid(alpha * g) * (u + 1),   g = min(gate, limit), u = clamp(up, -limit, limit)
 // for every expert, and the same with the weight sigmoid(shared gate logit) and its own limit for the shared expert.
+//
+// Options of the routing (MoeRouting; all off by default): the router may have more outputs than there are experts, the last
+// `identity` of them standing for experts whose output is the token's input itself (the sum of the chosen ones' weights goes
+// to id_weight[t], and the caller adds id_weight[t] * input[t]); a `correction` vector is added to the scores for the CHOICE
+// only (the weights stay the plain scores); the outputs form `group_count` equal groups of neighbours, a group's score is its
+// largest choice score, and only the outputs of the `group_keep` best groups can be chosen.  `act` 1: an expert is
+// weight * silu(gate) * up, without clamps.
 #include "common.cuh"
 
 SPY_MODULE(spy_moe)
 
 constexpr int MOE_MAX_EXPERTS = 1024;
 
+struct MoeRouting {
+    int identity;                  // router outputs behind the experts' that stand for identity experts
+    const float* correction;       // null, or [experts + identity]: added to the scores for the choice
+    int group_count, group_keep;   // 0: no groups
+    int act;                       // 0: clamped g * sigmoid(alpha g) * (u + 1); 1: silu(g) * u
+    float* id_weight;              // null, or [T]: the sum of the chosen identity experts' weights
+};
+
 template <typename TA, typename TO>
 __global__ void moe_activation_kernel(const TA* __restrict__ gu, long long gu_ld, const float* __restrict__ logits, long long logits_ld,
                                       TO* __restrict__ y, long long y_ld, int experts, int top, int ff, float limit, int shared_ff, float shared_limit,
-                                      float alpha, float* __restrict__ weights_out, int vec)
+                                      float alpha, float* __restrict__ weights_out, int vec, MoeRouting r)
 {
-    extern __shared__ float w_s[];                 // experts + 1 weights
+    extern __shared__ float w_s[];                 // total scores, the shared weight, total kept weights, total choice scores, the groups' scores
     __shared__ float scratch[33];
     pdl_enter();
     const int t = blockIdx.x, tid = threadIdx.x;
+    const int total = experts + r.identity;        // the router's outputs; the shared gate's logit lies behind them
     const float* lg = logits + (long long)t * logits_ld;
-    // softmax over all experts
+    float* kept_w = w_s + total + 1;               // kept_w[e]: the weight if chosen, else 0
+    float* choice = kept_w + total;                // the score the choice goes by
+    float* group_s = choice + total;
+    // softmax over all outputs
     float m = -INFINITY;
-    for (int e = tid; e < experts; e += blockDim.x) m = fmaxf(m, lg[e]);
+    for (int e = tid; e < total; e += blockDim.x) m = fmaxf(m, lg[e]);
     m = block_max(m, scratch);
     float s = 0.f;
-    for (int e = tid; e < experts; e += blockDim.x) s += expf(lg[e] - m);
+    for (int e = tid; e < total; e += blockDim.x) s += expf(lg[e] - m);
     s = block_sum(s, scratch);
-    for (int e = tid; e < experts; e += blockDim.x) w_s[e] = expf(lg[e] - m) / s;
+    for (int e = tid; e < total; e += blockDim.x) {
+        const float v = expf(lg[e] - m) / s;
+        w_s[e] = v;
+        choice[e] = r.correction != nullptr ? v + r.correction[e] : v;
+    }
     __syncthreads();
-    // the `top` largest stay: an expert stays when fewer than `top` experts beat it (a larger score, or an equal one at a lower index)
-    for (int e = tid; e < experts; e += blockDim.x) {
-        const float v = w_s[e];
+    if (r.group_count > 0) {
+        // a group's score is its largest choice score; a group stays when fewer than group_keep groups beat it
+        const int per = total / r.group_count;
+        for (int g = tid; g < r.group_count; g += blockDim.x) {
+            float best = -INFINITY;
+            for (int e = g * per; e < g * per + per; ++e) best = fmaxf(best, choice[e]);
+            group_s[g] = best;
+        }
+        __syncthreads();
+        for (int e = tid; e < total; e += blockDim.x) {
+            const int g = e / per;
+            const float v = group_s[g];
+            int ahead = 0;
+            for (int o = 0; o < r.group_count; ++o) {
+                const float x = group_s[o];
+                ahead += (x > v || (x == v && o < g)) ? 1 : 0;
+            }
+            if (ahead >= r.group_keep) choice[e] = -INFINITY;
+        }
+        __syncthreads();
+    }
+    // the `top` largest stay: an output stays when fewer than `top` beat it (a larger choice score, or an equal one at a lower index)
+    for (int e = tid; e < total; e += blockDim.x) {
+        const float v = choice[e];
         int ahead = 0;
-        for (int o = 0; o < experts; ++o) {
-            const float x = w_s[o];
+        for (int o = 0; o < total; ++o) {
+            const float x = choice[o];
             ahead += (x > v || (x == v && o < e)) ? 1 : 0;
         }
-        w_s[experts + 1 + e] = ahead < top ? v : 0.f;
+        kept_w[e] = (ahead < top && v > -INFINITY) ? w_s[e] : 0.f;
     }
-    if (tid == 0) w_s[experts] = shared_ff > 0 ? 1.0f / (1.0f + expf(-lg[experts])) : 0.f;
+    if (tid == 0) w_s[total] = shared_ff > 0 ? 1.0f / (1.0f + expf(-lg[total])) : 0.f;
     __syncthreads();
+    if (r.id_weight != nullptr && tid == 0) {
+        float idw = 0.f;
+        for (int e = experts; e < total; ++e) idw += kept_w[e];
+        r.id_weight[t] = idw;
+    }
     if (weights_out != nullptr)
-        for (int e = tid; e <= experts; e += blockDim.x) weights_out[(long long)t * (experts + 1) + e] = e < experts ? w_s[experts + 1 + e] : w_s[experts];
+        for (int e = tid; e <= total; e += blockDim.x) weights_out[(long long)t * (total + 1) + e] = e < total ? kept_w[e] : w_s[total];
     const TA* g_row = gu + (long long)t * gu_ld;
     TO* y_row = y + (long long)t * y_ld;
     const int routed = experts * ff;
@@ -57,8 +106,8 @@ __global__ void moe_activation_kernel(const TA* __restrict__ gu, long long gu_ld
                 float w, lim;
                 const TA* src;
                 int j, n;
-                if (i < routed) { const int e = i / ff; j = i - e * ff; n = ff; w = w_s[experts + 1 + e]; lim = limit; src = g_row + (long long)e * 2 * ff; }
-                else { j = i - routed; n = shared_ff; w = w_s[experts]; lim = shared_limit; src = g_row + (long long)routed * 2; }
+                if (i < routed) { const int e = i / ff; j = i - e * ff; n = ff; w = kept_w[e]; lim = limit; src = g_row + (long long)e * 2 * ff; }
+                else { j = i - routed; n = shared_ff; w = w_s[total]; lim = shared_limit; src = g_row + (long long)routed * 2; }
                 uint4 packed = make_uint4(0u, 0u, 0u, 0u);
                 if (w != 0.f) {
                     const uint4 gq = *reinterpret_cast<const uint4*>(src + j), uq = *reinterpret_cast<const uint4*>(src + n + j);
@@ -67,6 +116,11 @@ __global__ void moe_activation_kernel(const TA* __restrict__ gu, long long gu_ld
                     __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&packed);
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
+                        if (r.act == 1) {
+                            const float ga = __low2float(g2[q]), gb = __high2float(g2[q]);
+                            o2[q] = __floats2bfloat162_rn(w * (ga / (1.0f + expf(-ga))) * __low2float(u2[q]), w * (gb / (1.0f + expf(-gb))) * __high2float(u2[q]));
+                            continue;
+                        }
                         const float ga = fminf(__low2float(g2[q]), lim), gb = fminf(__high2float(g2[q]), lim);
                         const float ua = fminf(fmaxf(__low2float(u2[q]), -lim), lim), ub = fminf(fmaxf(__high2float(u2[q]), -lim), lim);
                         o2[q] = __floats2bfloat162_rn(w * (ga / (1.0f + expf(-alpha * ga))) * (ua + 1.0f), w * (gb / (1.0f + expf(-alpha * gb))) * (ub + 1.0f));
@@ -81,38 +135,94 @@ __global__ void moe_activation_kernel(const TA* __restrict__ gu, long long gu_ld
         float w, lim;
         const TA* src;
         int j, n;
-        if (i < routed) { const int e = i / ff; j = i - e * ff; n = ff; w = w_s[experts + 1 + e]; lim = limit; src = g_row + (long long)e * 2 * ff; }
-        else { j = i - routed; n = shared_ff; w = w_s[experts]; lim = shared_limit; src = g_row + (long long)routed * 2; }
-        float r = 0.f;
-        if (w != 0.f) {
+        if (i < routed) { const int e = i / ff; j = i - e * ff; n = ff; w = kept_w[e]; lim = limit; src = g_row + (long long)e * 2 * ff; }
+        else { j = i - routed; n = shared_ff; w = w_s[total]; lim = shared_limit; src = g_row + (long long)routed * 2; }
+        float res = 0.f;
+        if (w != 0.f && r.act == 1) {
+            const float g = to_f32(src[j]);
+            res = w * (g / (1.0f + expf(-g))) * to_f32(src[n + j]);
+        } else if (w != 0.f) {
             const float g = fminf(to_f32(src[j]), lim);
             const float u = fminf(fmaxf(to_f32(src[n + j]), -lim), lim);
-            r = w * (g / (1.0f + expf(-alpha * g))) * (u + 1.0f);
+            res = w * (g / (1.0f + expf(-alpha * g))) * (u + 1.0f);
         }
-        y_row[i] = from_f32<TO>(r);
+        y_row[i] = from_f32<TO>(res);
     }
 }
 
 // gu [T, gu_ld]: per expert [gate (ff) | up (ff)], then the shared expert's [gate (shared_ff) | up (shared_ff)];
 // logits [T, logits_ld] float32: the router's `experts` logits, then (with a shared expert) the shared gate's logit;
-// y [T, y_ld]: experts * ff + shared_ff columns; weights_out (optional) [T, experts + 1] float32 receives the weights.
-extern "C" int spy_moe_activation(const void* gu, int gu_dtype, long long gu_ld, const float* logits, long long logits_ld, void* y, int y_dtype,
-                                  long long y_ld, int tokens, int experts, int top, int ff, float limit, int shared_ff, float shared_limit, float alpha,
-                                  float* weights_out, cudaStream_t stream)
+// y [T, y_ld]: experts * ff + shared_ff columns; weights_out (optional) [T, experts + identity + 1] float32 receives the weights.
+static int run_moe_activation(const void* gu, int gu_dtype, long long gu_ld, const float* logits, long long logits_ld, void* y, int y_dtype,
+                              long long y_ld, int tokens, int experts, int top, int ff, float limit, int shared_ff, float shared_limit, float alpha,
+                              float* weights_out, MoeRouting r, cudaStream_t stream)
 {
     if (tokens <= 0) return 0;
-    if (experts <= 0 || experts > MOE_MAX_EXPERTS || top <= 0 || top > experts || ff <= 0 || shared_ff < 0)
-        SPY_FAIL("moe_activation: %d experts (at most %d), top %d, expert size %d, shared size %d", experts, MOE_MAX_EXPERTS, top, ff, shared_ff);
-    const size_t smem = (size_t)(2 * experts + 2) * sizeof(float);
+    const int total = experts + r.identity;
+    if (experts <= 0 || r.identity < 0 || total > MOE_MAX_EXPERTS || top <= 0 || top > total || ff <= 0 || shared_ff < 0)
+        SPY_FAIL("moe_activation: %d experts and %d identity experts (at most %d), top %d, expert size %d, shared size %d", experts, r.identity,
+                 MOE_MAX_EXPERTS, top, ff, shared_ff);
+    if (r.group_count < 0 || (r.group_count > 0 && (total % r.group_count != 0 || r.group_keep <= 0 || r.group_keep > r.group_count
+                                                    || (long long)r.group_keep * (total / r.group_count) < top)))
+        SPY_FAIL("moe_activation: %d groups of which %d are kept do not fit %d router outputs and top %d", r.group_count, r.group_keep, total, top);
+    if (r.act < 0 || r.act > 1) SPY_FAIL("moe_activation: activation code %d", r.act);
+    const size_t smem = (size_t)(3 * total + 1 + (r.group_count > 0 ? r.group_count : 0)) * sizeof(float);
     const int vec = gu_dtype == SPY_BF16 && y_dtype == SPY_BF16 && ff % 8 == 0 && shared_ff % 8 == 0 && gu_ld % 8 == 0 && y_ld % 8 == 0
                     && ((reinterpret_cast<uintptr_t>(gu) | reinterpret_cast<uintptr_t>(y)) & 15) == 0;
     SPY_DISPATCH_DTYPE(gu_dtype, TA, {
         SPY_DISPATCH_DTYPE(y_dtype, TO, {
             spy_launch(moe_activation_kernel<TA, TO>, dim3(tokens), dim3(256), smem, stream, (const TA*)gu, gu_ld, logits, logits_ld, (TO*)y, y_ld,
-                       experts, top, ff, limit, shared_ff, shared_limit, alpha, weights_out, vec);
+                       experts, top, ff, limit, shared_ff, shared_limit, alpha, weights_out, vec, r);
         })
     })
     SPY_CHECK_LAUNCH("moe_activation");
+    return 0;
+}
+
+extern "C" int spy_moe_activation(const void* gu, int gu_dtype, long long gu_ld, const float* logits, long long logits_ld, void* y, int y_dtype,
+                                  long long y_ld, int tokens, int experts, int top, int ff, float limit, int shared_ff, float shared_limit, float alpha,
+                                  float* weights_out, cudaStream_t stream)
+{
+    MoeRouting r = {0, nullptr, 0, 0, 0, nullptr};
+    return run_moe_activation(gu, gu_dtype, gu_ld, logits, logits_ld, y, y_dtype, y_ld, tokens, experts, top, ff, limit, shared_ff, shared_limit, alpha,
+                              weights_out, r, stream);
+}
+
+// The same with the routing's options (see the head of this file); logits hold experts + identity columns, then the shared gate's.
+extern "C" int spy_moe_activation_routed(const void* gu, int gu_dtype, long long gu_ld, const float* logits, long long logits_ld, void* y, int y_dtype,
+                                         long long y_ld, int tokens, int experts, int top, int ff, float limit, int shared_ff, float shared_limit,
+                                         float alpha, float* weights_out, int identity, const float* correction, int group_count, int group_keep, int act,
+                                         float* id_weight, cudaStream_t stream)
+{
+    MoeRouting r = {identity, correction, group_count, group_keep, act, id_weight};
+    return run_moe_activation(gu, gu_dtype, gu_ld, logits, logits_ld, y, y_dtype, y_ld, tokens, experts, top, ff, limit, shared_ff, shared_limit, alpha,
+                              weights_out, r, stream);
+}
+
+// out[t, :] += w[t] * x[t, :] in 32-bit (out float32): what the identity experts of a mixture contribute.
+template <typename TX>
+__global__ void add_scaled_rows_kernel(float* __restrict__ out, const TX* __restrict__ x, const float* __restrict__ w, int width, long long total)
+{
+    pdl_enter();
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (; i < total; i += stride) {
+        const float wt = w[i / width];
+        if (wt != 0.f) out[i] = fmaf(wt, to_f32(x[i]), out[i]);
+    }
+}
+
+extern "C" int spy_add_scaled_rows(float* out, const void* x, int x_dtype, const float* w, int tokens, int width, cudaStream_t stream)
+{
+    if (tokens <= 0 || width <= 0) return 0;
+    const long long total = (long long)tokens * width;
+    long long blocks = (total + 255) / 256;
+    const long long most = (long long)spy_sm_count() * 32;
+    if (blocks > most) blocks = most;
+    SPY_DISPATCH_DTYPE(x_dtype, TX, {
+        spy_launch(add_scaled_rows_kernel<TX>, dim3((int)blocks), dim3(256), 0, stream, out, (const TX*)x, w, width, total);
+    })
+    SPY_CHECK_LAUNCH("add_scaled_rows");
     return 0;
 }
 

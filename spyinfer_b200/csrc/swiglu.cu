@@ -154,6 +154,49 @@ extern "C" int spy_gated_activation(const void* gate_up, void* out, int dtype, i
     return 0;
 }
 
+// A clamped gated activation on a fused gate|up tensor with the projections' bias folded in (32-bit arithmetic):
+//   g = min(x[t, i] + b[i], limit), u = clamp(x[t, inter + i] + b[inter + i], -limit, limit), out[t, i] = g * sigmoid(alpha * g) * (u + 1).
+// bias: null or [2 * inter] float32.  TI, TO: the input's and the output's type (a 32-bit product may feed a bfloat16 activation).
+template <typename TI, typename TO>
+__global__ void clamped_glu_kernel(const TI* __restrict__ gate_up, const float* __restrict__ bias, TO* __restrict__ out, int inter, long long total,
+                                   float limit, float alpha)
+{
+    pdl_enter();
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (; i < total; i += stride) {
+        const long long row = i / inter;
+        const int col = (int)(i - row * inter);
+        const TI* src = gate_up + row * 2 * inter;
+        float g = to_f32(src[col]), u = to_f32(src[inter + col]);
+        if (bias != nullptr) {
+            g += bias[col];
+            u += bias[inter + col];
+        }
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        out[i] = from_f32<TO>(g / (1.0f + expf(-alpha * g)) * (u + 1.0f));
+    }
+}
+
+extern "C" int spy_clamped_glu(const void* gate_up, int in_dtype, const float* bias, void* out, int out_dtype, int tokens, int inter, float limit,
+                               float alpha, cudaStream_t stream)
+{
+    if (tokens <= 0) return 0;
+    if (inter <= 0 || !(limit > 0.f)) SPY_FAIL("clamped_glu: intermediate size %d, limit %g", inter, (double)limit);
+    const long long total = (long long)tokens * inter;
+    long long blocks = (total + 255) / 256;
+    const long long most = (long long)spy_sm_count() * 32;
+    if (blocks > most) blocks = most;
+    SPY_DISPATCH_DTYPE(in_dtype, TI, {
+        SPY_DISPATCH_DTYPE(out_dtype, TO, {
+            spy_launch(clamped_glu_kernel<TI, TO>, dim3((int)blocks), dim3(256), 0, stream, (const TI*)gate_up, bias, (TO*)out, inter, total, limit, alpha);
+        })
+    })
+    SPY_CHECK_LAUNCH("clamped_glu");
+    return 0;
+}
+
 // x[i] = cap * tanh(x[i] / cap) in place (32-bit): logits with a soft cap.
 __global__ void softcap_kernel(float* __restrict__ x, long long total, float cap)
 {

@@ -132,8 +132,9 @@ class Model:
     def cache_needs(self):
         """Per run-order entry: its mixer's need, and the entry whose cache it reads instead."""
         cache_of = [e.cache_of for e in self.spec.run_order]
-        needs = [self.layers[e.layer].block.cache_need() if e.cache_of is None else None
-                 for e in self.spec.run_order]               # an entry that reads another's cache keeps nothing of its own
+        # an entry that reads another's cache keeps nothing of its own, unless its arrangement says what it keeps beside it
+        needs = [self.layers[e.layer].block.cache_need() if e.cache_of is None else self.layers[e.layer].block.cache_need_reading()
+                 for e in self.spec.run_order]
         # what the embedding keeps between steps (a request's last token, if it looks at pairs of tokens) comes after the
         # run order's entries, as one more entry of the cache manager
         own = getattr(self.embedding, "cache_need", lambda: None)()

@@ -100,7 +100,7 @@ class ModelRunner:
         paged = [n for n in needs if isinstance(n, PagedCacheNeed)]
         windowed = [n for n in paged if n.window is not None] if any(n.window is None for n in paged) else []
         elt = torch.empty((), dtype=self.model.ctx.dtype).element_size()
-        fixed = sum(CacheManager.pages_of_group(n.window, page, 1 << 30, cfg.max_num_seqs, step) * n.planes * n.num_kv_heads * page * n.head_dim * elt
+        fixed = sum(CacheManager.pages_of_group(n.window, page, 1 << 30, cfg.max_num_seqs, step, 1, n.keep_first) * n.planes * n.num_kv_heads * page * n.head_dim * elt
                     for n in windowed)
         # the per-request states of recurrent parts (one row a slot and the spare one) are allocated beside the pages
         states = 0

@@ -178,11 +178,11 @@ def _stack_of(delta: Optional[torch.Tensor], like: torch.Tensor, what: str):
 
 def layernorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, delta: Optional[torch.Tensor] = None, delta_scale: float = 1.0,
               delta2: Optional[torch.Tensor] = None, delta2_scale: float = 1.0, rows: Optional[torch.Tensor] = None, write_back: bool = False,
-              center: bool = True) -> torch.Tensor:
-    """``out = layer_norm(x + delta_scale * delta + delta2_scale * delta2) * weight`` row by row (mean removed, no bias;
-    ``center=False``: the mean stays, an RMS norm); with ``write_back`` the sum is stored into ``x``; ``rows`` gathers rows.
-    Each delta has x's shape or is a stack ``[splits, rows, len]`` of partial sums that are added in order; both have
-    one dtype."""
+              center: bool = True, bias: Optional[torch.Tensor] = None, delta_weight: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out = layer_norm(x + delta_scale * delta_weight * delta + delta2_scale * delta2) * weight (+ bias)`` row by row (mean
+    removed; ``center=False``: the mean stays, an RMS norm); with ``write_back`` the sum is stored into ``x``; ``rows`` gathers
+    rows.  Each delta has x's shape or is a stack ``[splits, rows, len]`` of partial sums that are added in order; both have
+    one dtype.  ``bias`` and ``delta_weight`` (a multiplier along the row for ``delta``) are ``[len]`` of the weight's dtype."""
     _check(x, "layernorm input", ndim=2)
     _check(weight, "layernorm weight", ndim=1)
     _check(out, "layernorm output", ndim=2)
@@ -191,6 +191,13 @@ def layernorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tens
         raise KernelError(f"layernorm: row lengths differ: input {H}, weight {weight.shape[0]}, output {out.shape[1]}")
     if delta is None and delta2 is not None:
         delta, delta_scale, delta2, delta2_scale = delta2, delta2_scale, None, 1.0
+    for extra, what in ((bias, "layernorm bias"), (delta_weight, "layernorm delta weight")):
+        if extra is not None:
+            _check(extra, what, weight.dtype, 1)
+            if extra.shape[0] != H:
+                raise KernelError(f"{what}: {extra.shape[0]} elements for rows of {H}")
+    if delta_weight is not None and delta is None:
+        raise KernelError("layernorm: a delta weight without a delta")
     a, a_splits, a_stride = _stack_of(delta, x, "layernorm delta")
     b, b_splits, b_stride = _stack_of(delta2, x, "layernorm second delta")
     if a is not None and b is not None and a.dtype != b.dtype:
@@ -202,6 +209,12 @@ def layernorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tens
         n = x.shape[0]
     if out.shape[0] != n:
         raise KernelError(f"layernorm: output has {out.shape[0]} rows, expected {n}")
+    if bias is not None or delta_weight is not None:
+        _call("layernorm", "spy_layernorm_affine", _ptr(x), _code(x, "layernorm input"), _ptr(a), a_splits, ctypes.c_longlong(a_stride),
+              ctypes.c_float(delta_scale), _ptr(delta_weight), _ptr(b), b_splits, ctypes.c_longlong(b_stride), ctypes.c_float(delta2_scale),
+              _code(a, "layernorm delta") if a is not None else 0, _ptr(rows), _ptr(weight), _ptr(bias), _code(weight, "layernorm weight"), _ptr(out),
+              _code(out, "layernorm output"), n, H, ctypes.c_float(eps), int(bool(write_back)), int(bool(center)), _stream())
+        return out
     _call("layernorm", "spy_layernorm", _ptr(x), _code(x, "layernorm input"), _ptr(a), a_splits, ctypes.c_longlong(a_stride), ctypes.c_float(delta_scale),
           _ptr(b), b_splits, ctypes.c_longlong(b_stride), ctypes.c_float(delta2_scale), _code(a, "layernorm delta") if a is not None else 0,
           _ptr(rows), _ptr(weight), _code(weight, "layernorm weight"), _ptr(out), _code(out, "layernorm output"), n, H, ctypes.c_float(eps),
@@ -324,10 +337,11 @@ def qk_rope_store(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim
 
 def attention_generic(q: torch.Tensor, num_heads: int, head_dim: int, out: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor,
                       positions: torch.Tensor, seq_of_token: torch.Tensor, scale: float, window: Optional[int] = None,
-                      status: Optional[torch.Tensor] = None) -> torch.Tensor:
+                      status: Optional[torch.Tensor] = None, keep_first: int = 0, sink: bool = False) -> torch.Tensor:
     """Attention of every token of the batch over its sequence's pages (any mix of prompt
     portions and single tokens).  ``q [T, >= nh*hd]`` (only the first nh*hd columns are read),
-    ``out [T, nh*hd]``."""
+    ``out [T, nh*hd]``.  ``keep_first`` (with a window): the sequence's first so many keys stay visible;
+    ``sink``: one is added to the softmax's denominator."""
     _check(q, "attention queries", ndim=2)
     _check(out, "attention output", q.dtype, 2)
     _check(pages, "cache pages", ndim=5)
@@ -344,7 +358,8 @@ def attention_generic(q: torch.Tensor, num_heads: int, head_dim: int, out: torch
         raise KernelError("attention: positions and seq_of_token must have one entry per token")
     _call("attention_generic", "spy_attention_generic", _ptr(q), ctypes.c_longlong(q.shape[1]), _ptr(out), _code(q, "attention queries"),
           _ptr(pages), _code(pages, "cache pages"), _ptr(block_table), block_table.shape[1], page_size, num_pages, num_heads, nkv, head_dim,
-          _ptr(positions), _ptr(seq_of_token), T, int(window or 0), ctypes.c_float(scale), _ptr(status), _stream(), planes)
+          _ptr(positions), _ptr(seq_of_token), T, int(window or 0), ctypes.c_float(scale), _ptr(status), _stream(), planes, int(keep_first),
+          int(bool(sink)))
     return out
 
 
@@ -1122,6 +1137,74 @@ def diff_qkv_store(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, bias:
     return q_out
 
 
+def sink_qkv_store(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, q_weight: torch.Tensor, k_weight: Optional[torch.Tensor],
+                   temp: Optional[torch.Tensor], eps: float, rope_table: Optional[torch.Tensor], positions: torch.Tensor, seq_of_token: torch.Tensor,
+                   q_out: torch.Tensor, block_table: Optional[torch.Tensor], pages: Optional[torch.Tensor], heads: int, kv_heads: int, dim: int, vdim: int,
+                   hd: int, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The step ahead of the attention kernel for queries and keys that are normed over the whole projection.  ``proj [T, ld]``
+    holds, from the given columns, the queries (``heads`` x ``dim``), the keys (``kv_heads`` x ``dim``) and the values (``kv_heads``
+    x ``vdim``).  All of a token's queries together are brought to unit root mean square and multiplied by ``q_weight [heads dim]``,
+    the keys likewise with ``k_weight [kv_heads dim]``; the pairs ``(2i, 2i + 1)`` of every head are rotated by ``rope_table
+    [positions, r, 2]``; a query head is multiplied by ``temp[head]``; every value head is brought to unit root mean square over
+    ``vdim``.  ``q_out [T, heads hd]`` and ``pages [num_pages, 2, kv_heads, page_size, hd]`` get rows of ``hd`` with zeros behind their
+    content.  ``pages`` None: the layer reads another layer's keys and values, and only the queries are made."""
+    _check(proj, "projection", ndim=2)
+    _check(q_out, "queries", ndim=2)
+    _check(positions, "positions", torch.int32, 1)
+    _check(seq_of_token, "seq_of_token", torch.int32, 1)
+    _check(q_weight, "q norm weight", ndim=1)
+    T, ld = proj.shape
+    if tuple(q_out.shape) != (T, heads * hd) or positions.shape[0] != T or seq_of_token.shape[0] != T or q_weight.shape[0] != heads * dim:
+        raise KernelError(f"sink_qkv_store: queries {tuple(q_out.shape)} do not fit {heads} heads of rows {hd}, or the norm weight their {heads * dim} elements")
+    if q_col + heads * dim > ld:
+        raise KernelError("sink_qkv_store: the query columns do not fit the projection")
+    num_pages = page_size = table_width = 0
+    if pages is not None:
+        _check(pages, "cache pages", q_out.dtype, 5)
+        _check(block_table, "block table", torch.int32, 2)
+        _check(k_weight, "k norm weight", q_weight.dtype, 1)
+        num_pages, two, nkv, page_size, row = pages.shape
+        table_width = block_table.shape[1]
+        if two != 2 or nkv != kv_heads or row != hd or k_weight.shape[0] != kv_heads * dim or max(k_col + kv_heads * dim, v_col + kv_heads * vdim) > ld:
+            raise KernelError(f"sink_qkv_store: pages {tuple(pages.shape)} do not fit {kv_heads} key/value heads of rows {hd}, or the columns the projection")
+    if temp is not None:
+        _check(temp, "head temperatures", q_weight.dtype, 1)
+        if temp.shape[0] != heads:
+            raise KernelError("sink_qkv_store: one temperature a head")
+    rot_half = table_rows = 0
+    if rope_table is not None:
+        _check(rope_table, "rope table", torch.float32, 3)
+        table_rows, rot_half = rope_table.shape[0], rope_table.shape[1]
+    _call("sink_attention", "spy_sink_qkv_store", _ptr(proj), _code(proj, "projection"), ctypes.c_longlong(ld), int(q_col), int(k_col), int(v_col),
+          _ptr(q_weight), _ptr(k_weight if pages is not None else None), _ptr(temp), _code(q_weight, "q norm weight"), ctypes.c_float(eps), _ptr(rope_table),
+          rot_half, table_rows, _ptr(positions), _ptr(seq_of_token), _ptr(q_out), _code(q_out, "queries"), _ptr(block_table if pages is not None else None),
+          table_width, _ptr(pages), page_size, num_pages, T, int(heads), int(kv_heads), int(dim), int(vdim), int(hd), _ptr(status), _stream())
+    return q_out
+
+
+def sink_merge(q: torch.Tensor, num_heads: int, head_dim: int, out: torch.Tensor, lse: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor,
+               positions: torch.Tensor, seq_of_token: torch.Tensor, scale: float, window: Optional[int], keep_first: int, sink: bool,
+               status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Completes a window attention whose normalised result is in ``out [T, nh hd]`` and whose logarithms of the sums of
+    exponentials are in ``lse [T, nh]``: the keys of a sequence's first ``keep_first`` positions that lie before the window
+    join the softmax, and with ``sink`` one is added to its denominator.  ``out`` is rewritten in place."""
+    _check(q, "attention queries", ndim=2)
+    _check(out, "attention output", q.dtype, 2)
+    _check(lse, "logarithms of the sums", torch.float32, 2)
+    _check(pages, "cache pages", q.dtype, 5)
+    _check(block_table, "block table", torch.int32, 2)
+    _check(positions, "positions", torch.int32, 1)
+    _check(seq_of_token, "seq_of_token", torch.int32, 1)
+    T = q.shape[0]
+    num_pages, planes, nkv, page_size, hd = pages.shape
+    if planes != 2 or hd != head_dim or q.shape[1] < num_heads * hd or tuple(out.shape) != (T, num_heads * hd) or tuple(lse.shape) != (T, num_heads):
+        raise KernelError(f"sink_merge: q {tuple(q.shape)}, out {tuple(out.shape)}, lse {tuple(lse.shape)}, pages {tuple(pages.shape)} do not fit")
+    _call("sink_attention", "spy_sink_merge", _ptr(q), ctypes.c_longlong(q.shape[1]), _ptr(out), _code(q, "attention queries"), _ptr(lse), _ptr(pages),
+          _ptr(block_table), block_table.shape[1], page_size, num_pages, int(num_heads), nkv, hd, _ptr(positions), _ptr(seq_of_token), T, int(window or 0),
+          int(keep_first), int(bool(sink)), ctypes.c_float(scale), _ptr(status), _stream())
+    return out
+
+
 def diff_combine(attn: torch.Tensor, hd: int, gate: Optional[torch.Tensor], gate_col: int, out: torch.Tensor, heads: int, vdim: int, lam: float,
                  post: float, eps: float) -> torch.Tensor:
     """``out[t, h] = unit_rms(a1 - lam * a2) * post * sigmoid(gate[t, gate_col + h vdim ...])`` with ``a1``, ``a2`` the first
@@ -1199,30 +1282,68 @@ def selective_scan(x: torch.Tensor, dt_pre: torch.Tensor, dt_bias: torch.Tensor,
 
 
 def moe_activation(gate_up: torch.Tensor, logits: torch.Tensor, out: torch.Tensor, experts: int, top: int, ff: int, limit: float, shared_ff: int = 0,
-                   shared_limit: float = 0.0, alpha: float = 1.702, weights_out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Routing weights and expert activations of a mixture of experts in one pass.  ``logits [T, >= experts (+ 1)]`` float32:
-    the router's logits and, with a shared expert, its gate's logit behind them.  ``gate_up [T, 2 (experts ff + shared_ff)]``:
-    per expert ``[gate | up]``, the shared expert last.  ``out [T, experts ff + shared_ff]`` gets, per expert,
-    ``weight * g * sigmoid(alpha g) * (u + 1)`` with ``g = min(gate, limit)``, ``u = clamp(up, -limit, limit)``; the weight is the
-    expert's softmax score if it is among the token's ``top`` largest, else 0, and ``sigmoid`` of its logit for the shared expert."""
+                   shared_limit: float = 0.0, alpha: float = 1.702, weights_out: Optional[torch.Tensor] = None, identity: int = 0,
+                   correction: Optional[torch.Tensor] = None, groups: Optional[tuple] = None, activation: str = "clamped_swish",
+                   id_weight: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Routing weights and expert activations of a mixture of experts in one pass.  ``logits [T, >= experts + identity (+ 1)]``
+    float32: the router's logits and, with a shared expert, its gate's logit behind them.  ``gate_up [T, 2 (experts ff +
+    shared_ff)]``: per expert ``[gate | up]``, the shared expert last.  ``out [T, experts ff + shared_ff]`` gets, per expert,
+    ``weight * g * sigmoid(alpha g) * (u + 1)`` with ``g = min(gate, limit)``, ``u = clamp(up, -limit, limit)`` (``activation``
+    ``"silu"``: ``weight * silu(gate) * up``, no clamps); the weight is the expert's softmax score if it is among the token's
+    ``top`` chosen, else 0, and ``sigmoid`` of its logit for the shared expert.
+
+    The choice: the softmax runs over ``experts + identity`` router outputs, the last ``identity`` of which are experts that
+    return their input (``id_weight [T]`` float32 receives the sum of the chosen ones' weights); ``correction [experts +
+    identity]`` float32 is added to the scores for the choice only; ``groups = (count, keep)``: the outputs form ``count`` equal
+    groups of neighbours and only those of the ``keep`` groups with the largest best choice score can be chosen."""
     _check(gate_up, "expert gate|up", ndim=2)
     _check(logits, "router logits", torch.float32, 2)
     _check(out, "expert activations", ndim=2)
+    if activation not in ("clamped_swish", "silu"):
+        raise KernelError(f"moe_activation: unknown activation {activation!r}")
     T = gate_up.shape[0]
-    cols = experts * ff + shared_ff
-    if gate_up.shape[1] != 2 * cols or tuple(out.shape) != (T, cols) or logits.shape[0] != T or logits.shape[1] < experts + (1 if shared_ff else 0):
+    cols, total = experts * ff + shared_ff, experts + int(identity)
+    if gate_up.shape[1] != 2 * cols or tuple(out.shape) != (T, cols) or logits.shape[0] != T or logits.shape[1] < total + (1 if shared_ff else 0):
         raise KernelError(f"moe_activation: gate|up {tuple(gate_up.shape)}, logits {tuple(logits.shape)}, output {tuple(out.shape)} do not fit")
     if weights_out is not None:
         _check(weights_out, "routing weights", torch.float32, 2)
-        if tuple(weights_out.shape) != (T, experts + 1):
-            raise KernelError("moe_activation: the routing weights are [T, experts + 1]")
-    _call("moe", "spy_moe_activation", _ptr(gate_up), _code(gate_up, "expert gate|up"), ctypes.c_longlong(gate_up.shape[1]), _ptr(logits),
-          ctypes.c_longlong(logits.shape[1]), _ptr(out), _code(out, "expert activations"), ctypes.c_longlong(out.shape[1]), T, int(experts), int(top),
-          int(ff), ctypes.c_float(limit), int(shared_ff), ctypes.c_float(shared_limit), ctypes.c_float(alpha), _ptr(weights_out), _stream())
+        if tuple(weights_out.shape) != (T, total + 1):
+            raise KernelError("moe_activation: the routing weights are [T, router outputs + 1]")
+    if correction is not None:
+        _check(correction, "choice correction", torch.float32, 1)
+        if correction.shape[0] != total:
+            raise KernelError("moe_activation: the correction has one entry per router output")
+    if id_weight is not None:
+        _check(id_weight, "identity weights", torch.float32, 1)
+        if id_weight.shape[0] != T:
+            raise KernelError("moe_activation: one identity weight a token")
+    if identity and id_weight is None:
+        raise KernelError("moe_activation: identity experts need a place for their weights")
+    plain = not identity and correction is None and not groups and activation == "clamped_swish"
+    args = (_ptr(gate_up), _code(gate_up, "expert gate|up"), ctypes.c_longlong(gate_up.shape[1]), _ptr(logits),
+            ctypes.c_longlong(logits.shape[1]), _ptr(out), _code(out, "expert activations"), ctypes.c_longlong(out.shape[1]), T, int(experts), int(top),
+            int(ff), ctypes.c_float(limit), int(shared_ff), ctypes.c_float(shared_limit), ctypes.c_float(alpha), _ptr(weights_out))
+    if plain:
+        _call("moe", "spy_moe_activation", *args, _stream())
+    else:
+        count, keep = (int(groups[0]), int(groups[1])) if groups else (0, 0)
+        _call("moe", "spy_moe_activation_routed", *args, int(identity), _ptr(correction), count, keep, 1 if activation == "silu" else 0, _ptr(id_weight),
+              _stream())
     return out
 
 
-_GATED_ACTIVATIONS = ("silu", "gelu_tanh")
+def add_scaled_rows(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """``out[t] += w[t] * x[t]`` in place; out float32 ``[T, H]``, x ``[T, H]``, w float32 ``[T]``."""
+    _check(out, "row sum target", torch.float32, 2)
+    _check(x, "rows", ndim=2)
+    _check(w, "row weights", torch.float32, 1)
+    if tuple(x.shape) != tuple(out.shape) or w.shape[0] != out.shape[0]:
+        raise KernelError("add_scaled_rows: shapes do not fit")
+    _call("moe", "spy_add_scaled_rows", _ptr(out), _ptr(x), _code(x, "rows"), _ptr(w), out.shape[0], out.shape[1], _stream())
+    return out
+
+
+_GATED_ACTIVATIONS = ("silu", "gelu_tanh")      # and "clamped_swish" through ``clamped_glu``
 
 
 def gated_activation(gate_up: torch.Tensor, out: torch.Tensor, kind: str) -> torch.Tensor:
@@ -1236,6 +1357,23 @@ def gated_activation(gate_up: torch.Tensor, out: torch.Tensor, kind: str) -> tor
         raise KernelError(f"gated_activation: input {tuple(gate_up.shape)} and output {tuple(out.shape)} do not fit")
     _call("swiglu", "spy_gated_activation", _ptr(gate_up), _ptr(out), _code(gate_up, "gated activation input"), T, two_i // 2,
           _GATED_ACTIVATIONS.index(kind), _stream())
+    return out
+
+
+def clamped_glu(gate_up: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, limit: float, alpha: float = 1.702) -> torch.Tensor:
+    """``out[t, i] = g * sigmoid(alpha g) * (u + 1)`` with ``g = min(gate_up[t, i] + bias[i], limit)`` and ``u = clamp(gate_up[t, I + i]
+    + bias[I + i], -limit, limit)``; ``bias [2 I]`` float32 or None; input and output may differ in type."""
+    _check(gate_up, "gated activation input", ndim=2)
+    _check(out, "gated activation output", ndim=2)
+    T, two_i = gate_up.shape
+    if two_i % 2 != 0 or tuple(out.shape) != (T, two_i // 2):
+        raise KernelError(f"clamped_glu: input {tuple(gate_up.shape)} and output {tuple(out.shape)} do not fit")
+    if bias is not None:
+        _check(bias, "gate|up bias", torch.float32, 1)
+        if bias.shape[0] != two_i:
+            raise KernelError("clamped_glu: the bias has one entry per column of the input")
+    _call("swiglu", "spy_clamped_glu", _ptr(gate_up), _code(gate_up, "gated activation input"), _ptr(bias), _ptr(out), _code(out, "gated activation output"),
+          T, two_i // 2, ctypes.c_float(limit), ctypes.c_float(alpha), _stream())
     return out
 
 

@@ -476,3 +476,131 @@ class DifferentialAttention(Attention):
         o = torch.empty((T, self.heads * self.vd), dtype=x.dtype, device=x.device)
         kernels.diff_combine(maps, self.hd, proj, self.cols[3], o, self.heads, self.vd, self.lam, 1.0 - self.diff, self.eps)
         return self.o(o, defer=self.defer_output, out_dtype=self.output_dtype)
+
+
+@register_part("sink_window_attention")
+class SinkWindowAttention(Attention):
+    """Grouped-query attention over a sliding window that also keeps a sequence's first tokens in view, under a softmax with
+    a sink: a query at position ``i`` sees ``j <= i`` with ``i - j < window`` or ``j < keep_first`` (kept keys stay at their
+    true positions), and ``p_j = exp(s_j) / (1 + sum exp(s_j))`` when ``sink`` is set (a key of score 0 that has no value).
+    Queries and keys are normed over the WHOLE projection (one root mean square for all of a token's query heads together,
+    a weight of that size; the same for its keys), then rotated; ``s = q . k * scale * temp[head]`` with a learned number a
+    head; every value head is brought to unit root mean square over ``vdim`` (no weight) and cached so.
+
+    A layer that ``shares_cache`` has no key or value tensors: its run-order entry names the entry whose keys and values it
+    reads (``RunEntry.cache_of``), with queries, mask, temperatures and output projection of its own; ``cache_window`` /
+    ``cache_keep_first`` then tell the owning layer what its readers need kept (the widest window, the most kept tokens).
+
+    The attention kernels see rows of ``max(dim, vdim)`` rounded up to 8 (zeros behind a row's content).  On the bfloat16
+    path the window's keys run on the tensor-core kernels of ``attention``, which leave each row's logarithm of its sum of
+    exponentials, and ``sink_merge`` adds the kept first keys and the sink; the plain kernel does all of it in one pass.
+
+    params: ``hidden_size``, ``heads``, ``kv_heads``, ``dim``, ``vdim``, ``eps``, ``scale`` (None: ``dim^(-1/2)``), ``window``
+    (None: every earlier key), ``keep_first`` (default 0), ``sink`` (default true), ``temperature`` (default true),
+    ``shares_cache``, ``cache_window``, ``cache_keep_first``, ``position`` (a rotary part with the interleaved pairing, or None),
+    ``prefix``.  Tensors: ``q [heads dim, hidden]``, ``k [kv_heads dim, hidden]``, ``v [kv_heads vdim, hidden]``, ``q.norm [heads
+    dim]``, ``k.norm [kv_heads dim]``, ``temp [heads]``, ``o [hidden, heads vdim]``."""
+
+    graph_safe = True
+    any_head_dim = True
+
+    def __init__(self, params, ctx):
+        self.heads, self.groups = int(params["heads"]), int(params["kv_heads"])
+        self.d, self.vd, self.eps = int(params["dim"]), int(params["vdim"]), float(params["eps"])
+        if min(self.heads, self.groups, self.d, self.vd) <= 0:
+            raise ValueError("sink_window_attention: sizes must be positive")
+        row = (max(self.d, self.vd) + 7) // 8 * 8
+        base = dict(params)
+        base.update(num_heads=self.heads, num_kv_heads=self.groups, head_dim=row, qk_norm_eps=None, chunk=None)
+        if base.get("scale") is None:
+            base["scale"] = 1.0 / math.sqrt(float(self.d))
+        super().__init__(base, ctx)
+        self.mma = False                 # the plain kernel is the one that knows the kept keys and the sink
+        self.keep_first = int(params.get("keep_first") or 0)
+        if self.keep_first < 0 or (self.keep_first and self.window is None):
+            self.keep_first = max(self.keep_first, 0) if self.window is not None else 0     # without a window every key is seen anyway
+        self.sink, self.temperature = bool(params.get("sink", True)), bool(params.get("temperature", True))
+        self.shares_cache = bool(params.get("shares_cache", False))
+        self.cache_window = params.get("cache_window", self.window)
+        self.cache_keep_first = int(params.get("cache_keep_first", self.keep_first) or 0)
+        if self.position is not None and (self.position.pairing != "interleaved" or self.position.rotary_dim > self.d):
+            raise ValueError("sink_window_attention: the rotation pairs neighbouring elements and fits within a head")
+        self.n_q, self.n_k, self.n_v = self.heads * self.d, self.groups * self.d, self.groups * self.vd
+        self.q_norm_w = self.k_norm_w = self.temp = None
+
+    def weight_decls(self):
+        p, W = self.prefix, self.hidden
+        decls = [WeightDecl(p + "q", (self.n_q, W)), WeightDecl(p + "q.norm", (self.n_q,), init="one_plus_normal")]
+        if not self.shares_cache:
+            decls += [WeightDecl(p + "k", (self.n_k, W)), WeightDecl(p + "v", (self.n_v, W)), WeightDecl(p + "k.norm", (self.n_k,), init="one_plus_normal")]
+        if self.temperature:
+            decls.append(WeightDecl(p + "temp", (self.heads,), init="one_plus_normal"))
+        return decls + [WeightDecl(p + "o", (W, self.heads * self.vd))]
+
+    def bind(self, tensors):
+        p = self.prefix
+        rows = [tensors[p + "q"]] + ([] if self.shares_cache else [tensors[p + "k"], tensors[p + "v"]])
+        if len({t.dtype for t in rows}) > 1:
+            rows = [t.float() for t in rows]
+        self.qkv = Linear(torch.cat(rows, dim=0).contiguous() if len(rows) > 1 else rows[0], self.ctx.dtype)
+        o = tensors[p + "o"]
+        if self.hd != self.vd:           # the attention's rows are wider than a value: the matching columns of the output projection are zero
+            o = torch.nn.functional.pad(o.reshape(self.hidden, self.heads, self.vd), (0, self.hd - self.vd)).reshape(self.hidden, self.heads * self.hd).contiguous()
+        self.o = Linear(o, self.ctx.dtype)
+        names = ["q.norm"] + ([] if self.shares_cache else ["k.norm"]) + (["temp"] if self.temperature else [])
+        small = {n: tensors[p + n] for n in names}
+        if len({t.dtype for t in small.values()}) > 1:
+            small = {n: t.float() for n, t in small.items()}
+        self.q_norm_w, self.k_norm_w, self.temp = small["q.norm"].contiguous(), small.get("k.norm"), small.get("temp")
+
+    def modules(self):
+        mods = ["sink_attention", "attention_generic"] + (["attention_tc", "attention_decode"] if self.tc else []) + self.qkv.modules() + self.o.modules()
+        if self.position is not None:
+            mods += self.position.modules()
+        return mods
+
+    def linears(self):
+        return [self.qkv, self.o]
+
+    def cache_need(self):
+        if self.shares_cache:
+            return None
+        window = int(self.cache_window) if self.cache_window is not None else None
+        return PagedCacheNeed(self.groups, self.hd, window, keep_first=self.cache_keep_first if window is not None else 0)
+
+    def forward(self, x, batch, cache):
+        if self.rope_table is None and self.position is not None:
+            self.rope_table = self.position.rotation_table()
+        if cache.writes == self.shares_cache:
+            raise ValueError("sink_window_attention: a layer with key and value projections owns its cache, one without reads another layer's")
+        T = x.shape[0]
+        proj = self.qkv(x, out_dtype=torch.float32)          # the norms over the whole projection read it unrounded
+        q = torch.empty((T, self.nh * self.hd), dtype=x.dtype, device=x.device)
+        kernels.sink_qkv_store(proj, 0, self.n_q, self.n_q + self.n_k, self.q_norm_w, self.k_norm_w, self.temp, self.eps, self.rope_table,
+                               batch.positions, batch.seq_of_token, q, cache.block_table if cache.writes else None, cache.pages if cache.writes else None,
+                               self.heads, self.groups, self.d, self.vd, self.hd, status=batch.status)
+        out = torch.empty((T, self.nh * self.hd), dtype=x.dtype, device=x.device)
+        self.attend(q, out, batch, cache)
+        return self.o(out, defer=self.defer_output, out_dtype=self.output_dtype)
+
+    def attend(self, q, out, batch, cache):
+        if not (self.tc and cache.page_size in kernels.ATTENTION_TMA_PAGE_SIZES):
+            # the float32 path, and sizes or pages that the tensor-core kernels do not take: everything in one plain kernel
+            return kernels.attention_generic(q, self.nh, self.hd, out, cache.pages, cache.block_table, batch.positions, batch.seq_of_token, self.scale,
+                                             window=self.window, status=batch.status, keep_first=self.keep_first, sink=self.sink)
+        head = batch.num_seqs if batch.one_token_each else batch.one_token_head
+        if not (0 < head <= kernels.ATTENTION_DECODE_MAX_SEQS and head * self.nkv <= kernels.ATTENTION_DECODE_MAX_PAIRS
+                and kernels.attention_decode_takes(self.nh, self.nkv, self.hd, cache.page_size, q.dtype)):
+            head = 0
+        merges = self.sink or self.keep_first > 0
+        lse = torch.empty((q.shape[0], self.nh), dtype=torch.float32, device=q.device) if merges else None
+        if head:
+            kernels.attention_decode(q, self.nh, self.hd, out, cache.pages, cache.block_table[:head], batch.positions, batch.q_start[:head + 1], head,
+                                     self.scale, window=self.window, status=batch.status, lse=lse)
+        if head < batch.num_seqs:
+            kernels.attention_tc(q, self.nh, self.hd, out, cache.pages, cache.block_table[head:], batch.positions, batch.q_start[head:],
+                                 batch.num_seqs - head, self.scale, window=self.window, status=batch.status, lse=lse)
+        if merges:
+            kernels.sink_merge(q, self.nh, self.hd, out, lse, cache.pages, cache.block_table, batch.positions, batch.seq_of_token, self.scale,
+                               self.window, self.keep_first, self.sink, status=batch.status)
+        return out

@@ -44,6 +44,16 @@ class ScaledParts:
 
 
 @dataclass
+class ChannelScaled:
+    """A sublayer output that the stream takes multiplied element by element along the row: ``residual += y * weight``
+    with ``weight [size]`` (a layer scale).  ``y`` is ``[rows, size]`` or a stack ``[splits, rows, size]`` of float32 partial
+    products.  A norm that says ``takes_channel_scale`` forms the product in its own kernel."""
+
+    y: torch.Tensor
+    weight: torch.Tensor
+
+
+@dataclass
 class NormedDelta:
     """A sublayer output that is still to be normed, weighted and added: ``residual += scale * norm(y) * weight``, the norm
     being that of the part which made this record (and which the next norm of the same kind folds into its own launch).
@@ -87,6 +97,8 @@ class Part:
 class Norm(Part):
     #: True: ``forward_add`` also takes a ``ScaledParts`` as ``delta`` and a ``scale`` other than 1
     takes_scaled_parts: bool = False
+    #: True: ``forward_add`` also takes a ``ChannelScaled`` as ``delta``
+    takes_channel_scale: bool = False
 
     def forward(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         raise NotImplementedError
@@ -174,6 +186,12 @@ class Block:
         it (it then returns a ``CompositeCacheNeed`` and hands the mixer its part of the view)."""
         mixer = self.parts.get("mixer")
         return mixer.cache_need() if mixer is not None else None
+
+    def cache_need_reading(self):
+        """The layer's need when its run-order entry reads another entry's cache (``RunEntry.cache_of``): None, the whole
+        view is then the other entry's; or a need whose ``SharedCacheNeed`` part stands for the other entry's pages, for an
+        arrangement that keeps state of its own beside them."""
+        return None
 
     def settle(self, hidden: torch.Tensor, delta):
         """Adds what ``forward`` left pending to the stream (the model asks for this when something else is added to the

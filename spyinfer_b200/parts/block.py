@@ -88,30 +88,62 @@ class PostNormBlock(Block):
 class ScaledPreNormBlock(Block):
     """``h += m * mixer(norm(h)); h += m * ffn(norm(h))`` with one multiplier ``m`` (param ``residual_scale``) for both
     sums, and a layer may do without the feed-forward half.  Its norms must take a scale (``Norm.takes_scaled_parts``);
-    then the mixer may also hand over a weighted sum that is still to be formed (``ScaledParts``)."""
+    then the mixer may also hand over a weighted sum that is still to be formed (``ScaledParts``).
+
+    Optional parts: ``mixer_conv``, an input convolution over time between the first norm and the mixer (a part with
+    ``forward(x, batch, cache)`` and ``cache_need()``, such as ``causal_conv``: the mixer reads ``c(norm(h))``), and
+    ``mixer_scale`` / ``ffn_scale`` (``channel_scale``), a multiplier for every channel of a sublayer's output, which the
+    next norm of the stream applies inside its kernel (it must say ``takes_channel_scale``).  With a convolution the
+    layer's need is the composite (convolution state, the mixer's need), and a layer that reads another entry's cache
+    still keeps its own convolution state."""
 
     graph_safe = True
     required = ("mixer_norm", "mixer")
-    optional = ("ffn_norm", "feed_forward")
+    optional = ("ffn_norm", "feed_forward", "mixer_conv", "mixer_scale", "ffn_scale")
 
     def __init__(self, parts, params=None):
         super().__init__(parts, params)
         self.residual_scale = float(self.params.get("residual_scale", 1.0))
         if (self.ffn_norm is None) != (self.feed_forward is None):
             raise ValueError("block arrangement 'pre_norm_scaled': the feed-forward and its norm come together or not at all")
+        if self.ffn_scale is not None and self.feed_forward is None:
+            raise ValueError("block arrangement 'pre_norm_scaled': a scale of the feed-forward's output needs the feed-forward")
         for norm in (self.mixer_norm, self.ffn_norm):
             if norm is not None and not norm.takes_scaled_parts:
                 raise ValueError(f"block arrangement 'pre_norm_scaled': the norm {norm.kind!r} takes no scale")
+            if norm is not None and (self.mixer_scale is not None or self.ffn_scale is not None) and not norm.takes_channel_scale:
+                raise ValueError(f"block arrangement 'pre_norm_scaled': the norm {norm.kind!r} takes no per-channel multiplier")
         if hasattr(self.mixer, "scaled_parts_ok"):
-            self.mixer.scaled_parts_ok = self.ffn_norm is not None      # the sum is formed by this layer's second norm
+            self.mixer.scaled_parts_ok = self.ffn_norm is not None and self.mixer_scale is None      # the sum is formed by this layer's second norm
+        self._conv_state = self.mixer_conv is not None and self.mixer_conv.cache_need() is not None
+
+    def cache_need(self):
+        from ..config.spec import CompositeCacheNeed
+        own = self.mixer.cache_need()
+        if not self._conv_state:
+            return own
+        return CompositeCacheNeed((self.mixer_conv.cache_need(),) + ((own,) if own is not None else ()))
+
+    def cache_need_reading(self):
+        from ..config.spec import CompositeCacheNeed, SharedCacheNeed
+        if not self._conv_state:
+            return None
+        return CompositeCacheNeed((self.mixer_conv.cache_need(), SharedCacheNeed()))
 
     def forward(self, hidden, delta, batch, cache):
         x = self.mixer_norm.forward_add(hidden, delta, scale=self.residual_scale)
+        if self.mixer_conv is not None:
+            x = self.mixer_conv.forward(x, batch, cache.parts[0] if self._conv_state else None)
+        if self._conv_state:
+            cache = cache.parts[1] if len(cache.parts) > 1 else None
         a = self.mixer.forward(x, batch, cache)
+        if self.mixer_scale is not None:
+            a = self.mixer_scale.defer(a)
         if self.feed_forward is None:
             return hidden, a
         x = self.ffn_norm.forward_add(hidden, a, scale=self.residual_scale)
-        return hidden, self.feed_forward.forward(x)
+        f = self.feed_forward.forward(x)
+        return hidden, self.ffn_scale.defer(f) if self.ffn_scale is not None else f
 
 
 @register_block("sandwich_norm")

@@ -33,19 +33,37 @@ from .registry import register_part
 @register_part("expert_mixture")
 class ExpertMixture(FeedForward):
     """params: ``hidden_size``, ``experts``, ``top``, ``ff`` (an expert's inner size), ``limit``, ``shared_ff`` (0: no shared
-    expert), ``shared_limit``, ``slope`` (default 1.702), ``prefix``.  Tensors: ``router [experts, hidden]``,
-    ``e<i>.{gate,up} [ff, hidden]``, ``e<i>.down [hidden, ff]``, and with a shared expert ``shared.{gate,up,down}`` and
-    ``shared.sg [1, hidden]``."""
+    expert), ``shared_limit``, ``slope`` (default 1.702), ``prefix``; ``activation`` (``clamped_swish``, the default, or ``silu``:
+    ``W_down (silu(W_gate h) * W_up h)`` without clamps, ``limit`` then unused); and the options of the choice: ``identity``
+    (default 0: so many further router outputs, behind the experts', stand for experts without tensors that return their
+    input), ``correction`` (default false: a tensor ``correction [experts + identity]`` is added to the scores for the choice
+    only), ``groups`` (None or ``(count, keep)``: the router's outputs form ``count`` equal groups of neighbours, a group counts
+    by its best choice score, and only the ``keep`` best groups' outputs can be chosen).  Tensors: ``router [experts +
+    identity, hidden]``, ``e<i>.{gate,up} [ff, hidden]``, ``e<i>.down [hidden, ff]``, and with a shared expert
+    ``shared.{gate,up,down}`` and ``shared.sg [1, hidden]``."""
 
     graph_safe = True
 
     def __init__(self, params, ctx):
         super().__init__(params, ctx)
         self.hidden, self.experts, self.top, self.ff = int(params["hidden_size"]), int(params["experts"]), int(params["top"]), int(params["ff"])
-        self.limit, self.slope = float(params["limit"]), float(params.get("slope", 1.702))
+        self.slope = float(params.get("slope", 1.702))
         self.shared_ff, self.shared_limit = int(params.get("shared_ff") or 0), float(params.get("shared_limit") or 0.0)
-        if min(self.hidden, self.experts, self.top, self.ff) <= 0 or self.top > self.experts or self.shared_ff < 0:
+        self.limit = float(params.get("limit") or 0.0)
+        self.activation = params.get("activation", "clamped_swish")
+        self.identity, self.has_correction = int(params.get("identity") or 0), bool(params.get("correction", False))
+        self.groups = tuple(int(v) for v in params["groups"]) if params.get("groups") else None
+        self.outputs = self.experts + self.identity                 # the router's outputs
+        if min(self.hidden, self.experts, self.top, self.ff) <= 0 or self.top > self.outputs or self.shared_ff < 0 or self.identity < 0:
             raise ValueError(f"expert_mixture: {self.experts} experts of {self.ff}, top {self.top}, shared {self.shared_ff} are not served")
+        if self.activation not in ("clamped_swish", "silu") or (self.activation == "clamped_swish" and not self.limit > 0.0):
+            raise ValueError(f"expert_mixture: activation {self.activation!r} (clamped_swish with a positive limit, or silu)")
+        if self.groups is not None:
+            count, keep = self.groups
+            if count <= 0 or self.outputs % count or not 0 < keep <= count or keep * (self.outputs // count) < self.top:
+                raise ValueError(f"expert_mixture: {count} groups of which {keep} are kept do not fit {self.outputs} router outputs and top {self.top}")
+        self.plain_choice = not self.identity and not self.has_correction and self.groups is None and self.activation == "clamped_swish"
+        self.correction = None
         self.prefix = params.get("prefix", "")
         self.cols = self.experts * self.ff + self.shared_ff
         self.router = self.gate_up = self.down = None
@@ -57,7 +75,7 @@ class ExpertMixture(FeedForward):
 
     def weight_decls(self):
         p, W = self.prefix, self.hidden
-        decls = [WeightDecl(p + "router", (self.experts, W))]
+        decls = [WeightDecl(p + "router", (self.outputs, W))] + ([WeightDecl(p + "correction", (self.outputs,))] if self.has_correction else [])
         for e in range(self.experts):
             decls += [WeightDecl(f"{p}e{e}.gate", (self.ff, W)), WeightDecl(f"{p}e{e}.up", (self.ff, W)), WeightDecl(f"{p}e{e}.down", (W, self.ff))]
         if self.shared_ff:
@@ -77,6 +95,8 @@ class ExpertMixture(FeedForward):
         # the router (and the shared expert's gate behind it) in 32-bit
         routes = [tensors[p + "router"].float()] + ([tensors[p + "shared.sg"].float()] if self.shared_ff else [])
         self.router = Linear(torch.cat(routes, dim=0).contiguous(), self.ctx.dtype)
+        if self.has_correction:
+            self.correction = tensors[p + "correction"].float().contiguous()
 
     def modules(self):
         return ["moe"] + self.router.modules() + self.gate_up.modules() + self.down.modules()
@@ -85,13 +105,21 @@ class ExpertMixture(FeedForward):
         return [self.router, self.gate_up, self.down]
 
     def forward(self, x):
-        if 0 < self.routed_from <= x.shape[0] and self.top < self.experts and not torch.cuda.is_current_stream_capturing():
+        if self.plain_choice and 0 < self.routed_from <= x.shape[0] and self.top < self.experts and not torch.cuda.is_current_stream_capturing():
             return self._routed(x)
         logits = self.router(x, out_dtype=torch.float32)
         gu = self.gate_up(x)
         y = torch.empty((x.shape[0], self.cols), dtype=self.ctx.dtype, device=x.device)
-        kernels.moe_activation(gu, logits, y, self.experts, self.top, self.ff, self.limit, self.shared_ff, self.shared_limit, self.slope)
-        return self.down(y, defer=self.defer_output)
+        if self.plain_choice:
+            kernels.moe_activation(gu, logits, y, self.experts, self.top, self.ff, self.limit, self.shared_ff, self.shared_limit, self.slope)
+            return self.down(y, defer=self.defer_output)
+        idw = torch.empty((x.shape[0],), dtype=torch.float32, device=x.device) if self.identity else None
+        kernels.moe_activation(gu, logits, y, self.experts, self.top, self.ff, self.limit, self.shared_ff, self.shared_limit, self.slope,
+                               identity=self.identity, correction=self.correction, groups=self.groups, activation=self.activation, id_weight=idw)
+        if not self.identity:
+            return self.down(y, defer=self.defer_output)
+        # the identity experts' share, weight * input, joins the experts' sum in 32-bit
+        return kernels.add_scaled_rows(self.down(y, out_dtype=torch.float32), x, idw)
 
     def _routed(self, x):
         T, E, top, ff, sff, dev = x.shape[0], self.experts, self.top, self.ff, self.shared_ff, x.device

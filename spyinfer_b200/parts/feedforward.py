@@ -67,16 +67,22 @@ class MLP(FeedForward):
 @register_part("gated_mlp")
 class GatedMLP(FeedForward):
     graph_safe = True
-    """params: ``hidden_size``, ``intermediate_size``, ``activation`` (``silu``, or ``gelu_tanh``: the tanh form of gelu),
-    ``prefix``, ``names`` (the three tensors' names after the prefix: ``gate``, ``up``, ``down``; default ``gate_proj.weight``
-    and so on)."""
+    """params: ``hidden_size``, ``intermediate_size``, ``activation`` (``silu``; ``gelu_tanh``: the tanh form of gelu; or
+    ``clamped_swish``: ``g * sigmoid(slope g) * (u + 1)`` with ``g = min(gate, limit)``, ``u = clamp(up, -limit, limit)``, which
+    needs ``limit`` and takes ``slope``, default 1.702), ``bias`` (default false: the three projections have biases, named
+    as the weights with ``.b`` behind), ``prefix``, ``names`` (the three tensors' names after the prefix: ``gate``, ``up``,
+    ``down``; default ``gate_proj.weight`` and so on)."""
 
     def __init__(self, params, ctx):
         super().__init__(params, ctx)
         self.hidden, self.inter = int(params["hidden_size"]), int(params["intermediate_size"])
         self.activation = params.get("activation", "silu")
-        if self.activation not in kernels._GATED_ACTIVATIONS:
-            raise ValueError(f"gated_mlp: activation {self.activation!r} is not implemented ({', '.join(kernels._GATED_ACTIVATIONS)})")
+        if self.activation not in kernels._GATED_ACTIVATIONS + ("clamped_swish",):
+            raise ValueError(f"gated_mlp: activation {self.activation!r} is not implemented ({', '.join(kernels._GATED_ACTIVATIONS)}, clamped_swish)")
+        self.limit, self.slope, self.has_bias = float(params.get("limit") or 0.0), float(params.get("slope", 1.702)), bool(params.get("bias", False))
+        if self.activation == "clamped_swish" and not self.limit > 0.0:
+            raise ValueError("gated_mlp: the clamped activation needs a positive limit")
+        self.gate_up_bias = None
         self.prefix = params.get("prefix", "")
         self.names = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"}
         self.names.update(params.get("names") or {})
@@ -85,23 +91,29 @@ class GatedMLP(FeedForward):
 
     def weight_decls(self):
         p, n = self.prefix, self.names
-        return [WeightDecl(p + n["gate"], (self.inter, self.hidden)),
-                WeightDecl(p + n["up"], (self.inter, self.hidden)),
-                WeightDecl(p + n["down"], (self.hidden, self.inter))]
+        decls = [WeightDecl(p + n["gate"], (self.inter, self.hidden)),
+                 WeightDecl(p + n["up"], (self.inter, self.hidden)),
+                 WeightDecl(p + n["down"], (self.hidden, self.inter))]
+        if self.has_bias:
+            decls += [WeightDecl(p + n["gate"] + ".b", (self.inter,)), WeightDecl(p + n["up"] + ".b", (self.inter,)), WeightDecl(p + n["down"] + ".b", (self.hidden,))]
+        return decls
 
     def bind(self, tensors):
         p, n = self.prefix, self.names
         gate, up = tensors[p + n["gate"]], tensors[p + n["up"]]
         if gate.dtype != up.dtype:
             gate, up = gate.float(), up.float()
-        self.fused = (self.ctx.dtype == torch.bfloat16 and gate.dtype == torch.bfloat16 and self.activation in ("silu", "gelu_tanh")
+        self.fused = (self.ctx.dtype == torch.bfloat16 and gate.dtype == torch.bfloat16 and self.activation in ("silu", "gelu_tanh") and not self.has_bias
                       and kernels.tensor_core_gemm_takes(2 * self.inter, self.hidden))
         if self.fused:
             # rows alternate gate_i, up_i: the tensor-core product applies act(gate) * up in its epilogue
             self.gate_up = Linear(torch.stack([gate, up], dim=1).reshape(2 * self.inter, self.hidden).contiguous(), self.ctx.dtype)
         else:
             self.gate_up = Linear(torch.cat([gate, up], dim=0).contiguous(), self.ctx.dtype)
-        self.down = Linear(tensors[p + n["down"]], self.ctx.dtype)
+        if self.has_bias:
+            # the gate and up biases are added by the activation's kernel (32-bit), the down bias by a pass behind its product
+            self.gate_up_bias = torch.cat([tensors[p + n["gate"] + ".b"].float(), tensors[p + n["up"] + ".b"].float()]).contiguous()
+        self.down = Linear(tensors[p + n["down"]], self.ctx.dtype, bias=tensors[p + n["down"] + ".b"].float().contiguous() if self.has_bias else None)
         self.gate_up.hint_next = not self.fused       # fused: the down product follows at once
 
     def linears(self):
@@ -113,8 +125,13 @@ class GatedMLP(FeedForward):
     def forward(self, x):
         if self.fused:
             return self.down(self.gate_up(x, epilogue="swiglu" if self.activation == "silu" else "geglu_tanh"), defer=self.defer_output)
-        gu = self.gate_up(x)
         z = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
+        if self.activation == "clamped_swish":
+            kernels.clamped_glu(self.gate_up(x, out_dtype=torch.float32), self.gate_up_bias, z, self.limit, self.slope)     # biases and clamps meet the unrounded products
+            return self.down(z, defer=self.defer_output)
+        gu = self.gate_up(x)
+        if self.has_bias:
+            kernels.add_bias(gu, self.gate_up_bias)
         if self.activation == "silu":
             kernels.swiglu(gu, z)
         else:

@@ -11,7 +11,7 @@ import torch
 
 from .. import kernels
 from ..weights.loader import WeightDecl
-from .base import Norm, NormedDelta, ScaledParts
+from .base import ChannelScaled, Norm, NormedDelta, ScaledParts
 from .registry import register_part
 
 
@@ -62,34 +62,42 @@ class RMSNorm(Norm):
 
 @register_part("layer_norm")
 class LayerNorm(Norm):
-    """``(x - mean) / sqrt(var + eps) * weight`` with ``var`` the mean squared deviation, statistics in 32-bit, a plain
-    weight and no bias.  params: ``size``, ``eps``, ``weight`` (the tensor's relative name), ``center`` (default true;
-    false keeps the mean: an RMS norm).  The residual sum fused into the kernel may carry a scale and may be a weighted
-    sum of two results (``ScaledParts``): ``residual += scale * (s1 * d1 + s2 * d2)``."""
+    """``(x - mean) / sqrt(var + eps) * weight (+ bias)`` with ``var`` the mean squared deviation, statistics in 32-bit, a
+    plain weight.  params: ``size``, ``eps``, ``weight`` (the tensor's relative name), ``bias`` (a relative name, or None:
+    no bias), ``center`` (default true; false keeps the mean: an RMS norm).  The residual sum fused into the kernel may carry
+    a scale and may be a weighted sum of two results (``ScaledParts``): ``residual += scale * (s1 * d1 + s2 * d2)``, or one
+    result times a vector along the row (``ChannelScaled``): ``residual += scale * weight * d``."""
 
     graph_safe = True
     takes_scaled_parts = True
+    takes_channel_scale = True
     kernel_modules = ("layernorm",)
 
     def __init__(self, params, ctx):
         super().__init__(params, ctx)
         self.size, self.eps, self.weight_name = int(params["size"]), float(params["eps"]), params.get("weight", "weight")
         self.center = bool(params.get("center", True))
-        self.weight = None
+        self.bias_name = params.get("bias")
+        self.weight = self.bias = None
 
     def weight_decls(self):
-        return [WeightDecl(self.weight_name, (self.size,), init="one_plus_normal")]
+        return [WeightDecl(self.weight_name, (self.size,), init="one_plus_normal")] + ([WeightDecl(self.bias_name, (self.size,))] if self.bias_name else [])
 
     def bind(self, tensors):
         self.weight = tensors[self.weight_name]
+        if self.bias_name:
+            self.bias = tensors[self.bias_name].to(self.weight.dtype).contiguous()
 
     def forward(self, x, out_dtype=None):
         out = torch.empty(x.shape, dtype=out_dtype or self.ctx.dtype, device=x.device)
-        return kernels.layernorm(x, self.weight, self.eps, out, center=self.center)
+        return kernels.layernorm(x, self.weight, self.eps, out, center=self.center, bias=self.bias)
 
     def forward_add(self, residual, delta, rows=None, out_dtype=None, scale=1.0):
         n = residual.shape[0] if rows is None else rows.shape[0]
         out = torch.empty((n, self.size), dtype=out_dtype or self.ctx.dtype, device=residual.device)
+        if isinstance(delta, ChannelScaled):
+            return kernels.layernorm(residual, self.weight, self.eps, out, delta=delta.y, delta_scale=scale, delta_weight=delta.weight.to(self.weight.dtype),
+                                     rows=rows, write_back=rows is None, center=self.center, bias=self.bias)
         terms = delta.terms if isinstance(delta, ScaledParts) else ([(delta, 1.0)] if delta is not None else [])
         if len(terms) > 2:
             raise ValueError(f"layer_norm: a weighted sum of {len(terms)} results (at most two)")
@@ -97,7 +105,30 @@ class LayerNorm(Norm):
             terms = [(t.float() if t.dim() == 2 else t, s) for t, s in terms]
         (d1, s1), (d2, s2) = (terms + [(None, 1.0), (None, 1.0)])[:2]
         return kernels.layernorm(residual, self.weight, self.eps, out, delta=d1, delta_scale=scale * s1, delta2=d2, delta2_scale=scale * s2,
-                                 rows=rows, write_back=bool(terms) and rows is None, center=self.center)
+                                 rows=rows, write_back=bool(terms) and rows is None, center=self.center, bias=self.bias)
+
+
+@register_part("channel_scale")
+class ChannelScale(Norm):
+    """A learned multiplier for every channel of a sublayer's output (a layer scale): ``y * weight``.  It launches nothing:
+    ``defer(y)`` hands the product on as a ``ChannelScaled`` record that the next norm of the stream forms inside its own
+    kernel, in 32-bit.  params: ``size``, ``weight`` (the tensor's relative name)."""
+
+    graph_safe = True
+
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        self.size, self.weight_name = int(params["size"]), params.get("weight", "weight")
+        self.weight = None
+
+    def weight_decls(self):
+        return [WeightDecl(self.weight_name, (self.size,), init="one_plus_normal")]
+
+    def bind(self, tensors):
+        self.weight = tensors[self.weight_name].contiguous()
+
+    def defer(self, y):
+        return ChannelScaled(y, self.weight)
 
 
 @register_part("group_rms_norm")
