@@ -65,22 +65,38 @@ def keys_and_values(h, m, W, p, eps, positions):
     return k, v
 
 
-def sink_softmax_attention(q, k, v, scale, temp, size, keep_first):
-    """q [T, H, d], k [T, G, d], v [T, G, vd]; weights exp(s) / (1 + sum exp(s)) over the visible keys."""
+def visibility(T, size, keep_first):
+    """[query, key] of ``visible`` for a sequence of T tokens."""
+    i, j = torch.arange(T)[:, None], torch.arange(T)[None, :]
+    seen = j <= i
+    if size is not None:
+        seen = seen & ((i - j < size) | (j < keep_first))
+    return seen
+
+
+def sink_softmax_attention(q, k, v, scale, temp, size, keep_first, probs=None):
+    """q [T, H, d], k [T, G, d], v [T, G, vd]; weights exp(s) / (1 + sum exp(s)) over the visible keys (the one in the
+    denominator is a sink: a key of score 0 that has no value).  ``probs`` (a list) receives the weights [H, T, T]."""
     T, H = q.shape[0], q.shape[1]
     G = k.shape[1]
+    seen = visibility(T, size, keep_first)
     out = torch.zeros(T, H, v.shape[2], dtype=F)
+    kept = []
     for hh in range(H):
         g = hh // (H // G)
         s = (q[:, hh] @ k[:, g].T) * scale * temp[hh]
-        for i in range(T):
-            js = [j for j in range(T) if visible(i, j, size, keep_first)]
-            e = torch.exp(s[i, js])
-            out[i, hh] = (e / (1.0 + e.sum())) @ v[js, g]
+        s = torch.where(seen, s, torch.full_like(s, -math.inf))
+        m = torch.clamp(s.max(-1, keepdim=True).values, min=0.0)          # the sink's score is 0
+        e = torch.exp(s - m)
+        p = e / (torch.exp(-m) + e.sum(-1, keepdim=True))
+        out[:, hh] = p @ v[:, g]
+        kept.append(p)
+    if probs is not None:
+        probs.append(torch.stack(kept))
     return out
 
 
-def attention_mixer(h, m, W, p, eps, positions, shared=None):
+def attention_mixer(h, m, W, p, eps, positions, shared=None, probs=None):
     """``shared``: (keys, values) of the layer that ``kv_from`` names, or None for a layer with projections of its own.
     Returns the mixer's output and the (keys, values) it used."""
     T, H, d = h.shape[0], m["heads"], m["dim"]
@@ -89,7 +105,7 @@ def attention_mixer(h, m, W, p, eps, positions, shared=None):
     q = rotate_pairs(q.reshape(T, H, d), positions, int(rot.get("dims") or 0), rot.get("base", 1.0))
     kv = shared if shared is not None else keys_and_values(h, m, W, p, eps, positions)
     mask = m.get("mask") or {}
-    o = sink_softmax_attention(q, kv[0], kv[1], float(m["scale"]), W[p + "temp"], mask.get("size"), int(mask.get("keep_first") or 0))
+    o = sink_softmax_attention(q, kv[0], kv[1], float(m["scale"]), W[p + "temp"], mask.get("size"), int(mask.get("keep_first") or 0), probs)
     return o.reshape(T, -1) @ W[p + "o"].T, kv
 
 
@@ -137,8 +153,9 @@ def mixture_ff(h, mlp, W, p):
     return out
 
 
-def forward(cfg, W, tokens, return_layers=False):
-    """Logits [T, vocab] of one sequence (and, asked for, the stream after every layer)."""
+def forward(cfg, W, tokens, return_layers=False, probs=None):
+    """Logits [T, vocab] of one sequence (and, asked for, the stream after every layer; ``probs``, a list, receives every
+    layer's attention weights)."""
     eps, taps = float(cfg["norm"]["eps"]), int((cfg.get("canon") or {}).get("taps") or 0)
     positions = torch.arange(len(tokens))
     x = W["embed"][torch.tensor(tokens)] * float((cfg.get("embedding") or {}).get("scale", 1.0))
@@ -148,7 +165,7 @@ def forward(cfg, W, tokens, return_layers=False):
         h = layer_norm(x, W[p + "norm1"], W[p + "norm1.b"], eps)
         if taps:
             h = h + time_conv(h, W[p + "canon1"])
-        a, caches[i] = attention_mixer(h, m, W, p + "mix.", eps, positions, caches[m["kv_from"]] if m.get("kv_from") is not None else None)
+        a, caches[i] = attention_mixer(h, m, W, p + "mix.", eps, positions, caches[m["kv_from"]] if m.get("kv_from") is not None else None, probs)
         x = x + a * W[p + "ls1"]
         mlp = layer.get("mlp")
         if mlp is not None:
@@ -158,3 +175,70 @@ def forward(cfg, W, tokens, return_layers=False):
         streams.append(x.clone())
     logits = layer_norm(x, W["final.norm"], W["final.norm.b"], eps) @ W["embed"].T
     return (logits, torch.stack(streams)) if return_layers else logits
+
+
+# ---- what a checkpoint of a configuration holds, and seeded random ones ------------------------------------
+
+def tensor_shapes(cfg):
+    W, V = int(cfg["width"]), int(cfg["vocab"])
+    taps = int((cfg.get("canon") or {}).get("taps") or 0)
+    out = {"embed": (V, W), "final.norm": (W,), "final.norm.b": (W,)}
+    for i, layer in enumerate(cfg["layers"]):
+        p, m, mlp = f"l{i}.", layer["mixer"], layer.get("mlp")
+        out.update({p + "norm1": (W,), p + "norm1.b": (W,), p + "ls1": (W,)})
+        if taps:
+            out[p + "canon1"] = (W, taps)
+        H, G, d, vd = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+        out.update({p + "mix.q": (H * d, W), p + "mix.q.norm": (H * d,), p + "mix.temp": (H,), p + "mix.o": (W, H * vd)})
+        if m.get("kv_from") is None:
+            out.update({p + "mix.k": (G * d, W), p + "mix.v": (G * vd, W), p + "mix.k.norm": (G * d,)})
+        if mlp is None:
+            continue
+        out.update({p + "norm2": (W,), p + "norm2.b": (W,), p + "ls2": (W,)})
+        if mlp["kind"] == "dense":
+            ff = mlp["ff"]
+            out.update({p + "mlp.gate": (ff, W), p + "mlp.gate.b": (ff,), p + "mlp.up": (ff, W), p + "mlp.up.b": (ff,), p + "mlp.down": (W, ff),
+                        p + "mlp.down.b": (W,)})
+        else:
+            r, ff = mlp["router"], mlp["expert"]["ff"]
+            total = r["experts"] + int(r.get("identity") or 0)
+            out.update({p + "mlp.router": (total, W), p + "mlp.correction": (total,)})
+            for e in range(r["experts"]):
+                out.update({f"{p}mlp.e{e}.gate": (ff, W), f"{p}mlp.e{e}.up": (ff, W), f"{p}mlp.e{e}.down": (W, ff)})
+            if mlp.get("shared"):
+                sf = mlp["shared"]["ff"]
+                out.update({p + "mlp.shared.gate": (sf, W), p + "mlp.shared.up": (sf, W), p + "mlp.shared.down": (W, sf), p + "mlp.shared.sg": (1, W)})
+    return out
+
+
+def random_weights(cfg, seed, gain=1.0):
+    """Seeded weights in bfloat16 (as a checkpoint stores them): matrices of a size that keeps activations of order one, norm
+    weights, layer scales and temperatures around one, small biases and corrections."""
+    g = torch.Generator().manual_seed(seed)
+    out = {}
+    for name, shape in tensor_shapes(cfg).items():
+        last = name.rsplit(".", 1)[-1]
+        if name == "embed":
+            t = torch.randn(shape, generator=g)
+        elif last in ("norm1", "norm2", "norm") or name.endswith((".q.norm", ".k.norm")):
+            t = 1.0 + 0.2 * torch.randn(shape, generator=g)
+        elif last in ("ls1", "ls2"):
+            t = 0.6 + 0.2 * torch.randn(shape, generator=g)
+        elif last == "temp":
+            t = 1.0 + 0.3 * torch.rand(shape, generator=g)
+        elif last == "b":
+            t = 0.2 * torch.randn(shape, generator=g)
+        elif last == "correction":
+            t = 0.05 * torch.randn(shape, generator=g)
+        elif last == "canon1":
+            t = 0.4 * torch.randn(shape, generator=g)
+        elif last == "router" or last == "sg":
+            t = gain * 2.0 * torch.randn(shape, generator=g) / math.sqrt(shape[-1])
+        else:
+            t = gain * torch.randn(shape, generator=g) / math.sqrt(shape[-1])
+        out[name] = t.to(torch.bfloat16)
+    return out
+
+
+def as_float64(W):
+    return {k: v.to(F) for k, v in W.items()}
