@@ -3,7 +3,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--shape 8b|14b|32b] [--batch B] [--context C] [--impl ours|reference]
     python bench.py --workload mixed [--shape 14b] [--requests 64] [--budget 2048]     (a continuous batch through LLMEngine; its own line)
-    python bench.py --workload nezolorn | daronex | naforax [--layers 6] [--prefill-tokens 2048]   (another design beside Qwen3 at equal layer sizes; its own line)
+    python bench.py --workload nezolorn | daronex | naforax | dogilorn [--layers 6] [--prefill-tokens 2048]   (another design beside Qwen3 at equal layer sizes; its own line)
 
 The model has the layer sizes of Qwen3-8B (36 layers, hidden 4096, 32 query heads, 8 key/value
 heads, head size 128, intermediate 12288, vocabulary 151936, untied head) with seeded random
@@ -704,6 +704,86 @@ def naforax_workload(args) -> int:
     return 0
 
 
+def dogilorn_workload(args) -> int:
+    """``--workload dogilorn``: prefill and decode throughput of the Dogilorn design (attention over a window that keeps a
+    sequence's first tokens in view, with a sink in its softmax, queries and keys normed over the whole projection, every third
+    layer reading the keys and values of the layer before it; layer norms with bias, layer scale, an input convolution; dense
+    clamped feed-forwards and expert mixtures with grouped choice and identity experts) at two layer sizes that resemble real
+    models, beside the engine's Qwen3 model with the same width, heads, head size, feed-forward size, vocabulary, number of
+    layers and the same sliding window on every layer, all with seeded random weights in bfloat16.  Measured as ``--workload
+    nezolorn`` is: one prompt of ``--prefill-tokens`` tokens, decoding at batch 8 and 64 from ``--context`` tokens through the
+    decode graphs, and each kernel's time inside one prompt step and one decode step of batch 64."""
+    hbm_gbs, bf16_tflops, _, peak_src = peaks()
+    layers, vocab, page = args.layers or 6, 32000, 16
+    T, ctx = args.prefill_tokens, min(args.context, 4096)
+    window, keep = 1024, 4
+    sizes = {"width2048": dict(width=2048, heads=16, kv=4, hd=128, ff=8192, experts=6, identity=2, top=2, groups=(4, 2), expert_ff=2048, shared_ff=4096),
+             "width4096": dict(width=4096, heads=32, kv=8, hd=128, ff=12288, experts=6, identity=2, top=2, groups=(4, 2), expert_ff=3072, shared_ff=6144)}
+
+    def configs(z):
+        dense = {"kind": "dense", "ff": z["ff"], "limit": 7.0}
+        moe = {"kind": "moe", "router": {"experts": z["experts"], "identity": z["identity"], "top": z["top"],
+                                         "groups": {"count": z["groups"][0], "keep": z["groups"][1]}},
+               "expert": {"ff": z["expert_ff"]}, "shared": {"ff": z["shared_ff"]}}
+
+        def layer(i):
+            mixer = {"heads": z["heads"], "kv_heads": z["kv"], "dim": z["hd"], "vdim": z["hd"], "scale": z["hd"] ** -0.5,
+                     "mask": {"size": window, "keep_first": keep}, "rot": {"base": 500000.0, "dims": 64}}
+            if i % 3 == 2:
+                mixer["kv_from"] = i - 1
+            return {"type": "attention", "mixer": mixer, "mlp": dense if i % 2 == 0 else moe}
+
+        dg = {"architecture": "Dogilorn", "vocab": vocab, "width": z["width"], "norm": {"eps": 1e-5}, "canon": {"taps": 4}, "embedding": {"scale": 2.0},
+              "layers": [layer(i) for i in range(layers)]}
+        qw = dict(QWEN3_8B)
+        qw.update({"num_hidden_layers": layers, "hidden_size": z["width"], "num_attention_heads": z["heads"], "num_key_value_heads": z["kv"],
+                   "head_dim": z["hd"], "intermediate_size": z["ff"], "vocab_size": vocab, "use_sliding_window": True, "sliding_window": window,
+                   "max_window_layers": 0})
+        return {"dogilorn": dg, "qwen3": qw}
+
+    def measure(cfg_json, z, name):
+        def annotate(res, rate):
+            W, H, hd = z["width"], z["heads"], z["hd"]
+            keys = sum(min(p + 1, window) for p in range(T))
+            rate("kernels_prefill", "attention_tc.spy_attention_tc" + ("_lse" if name == "dogilorn" else ""), flops=4.0 * keys * H * hd * layers)
+            rate("kernels_decode_b64", "attention_decode.spy_attention_decode" + ("_lse" if name == "dogilorn" else ""),
+                 nbytes=64.0 * z["kv"] * min(ctx + 1, window) * hd * 2 * 2 * layers)
+            for block, rows in (("kernels_prefill", T), ("kernels_decode_b64", 64)):
+                if name == "dogilorn":
+                    n_own = sum(1 for i in range(layers) if i % 3 != 2)
+                    n_moe, n_dense = layers // 2, layers - layers // 2
+                    # reads the sublayer's output (16-bit, or 32-bit behind a mixture) and the stream, writes the stream and the normed row
+                    rate(block, "layernorm.spy_layernorm_affine", nbytes=float(2 * layers) * rows * W * (2 + 4 + 4 + 2))
+                    rate(block, "time_conv.spy_time_conv", nbytes=float(layers) * rows * W * 4)
+                    # reads the 32-bit projection, writes the queries and (layers with keys of their own) a key and a value row
+                    rate(block, "sink_attention.spy_sink_qkv_store",
+                         nbytes=float(rows) * (layers * H * hd * 6 + n_own * 2 * z["kv"] * hd * 6))
+                    rate(block, "sink_attention.spy_sink_merge", nbytes=float(layers) * rows * H * hd * (2 + 2 + 2))
+                    rate(block, "swiglu.spy_clamped_glu", nbytes=float(n_dense) * rows * z["ff"] * (8 + 2))
+                    cols = z["experts"] * z["expert_ff"] + z["shared_ff"]
+                    rate(block, "moe.spy_moe_activation_routed", nbytes=float(n_moe) * rows * ((z["top"] * z["expert_ff"] + z["shared_ff"]) * 4 + cols * 2))
+                else:
+                    rate(block, "rmsnorm.spy_rmsnorm", nbytes=float(2 * layers) * rows * W * (4 + 4 + 4 + 2))
+                    rate(block, "qk_rope_store.spy_qk_rope_store", nbytes=float(layers) * rows * (H + 2 * z["kv"]) * hd * 4)
+
+        return _measure_design(args, cfg_json, vocab, page, T, ctx, annotate)
+
+    out_sizes = {}
+    with ClockSampler() as clocks:
+        for tag, z in sizes.items():
+            out_sizes[tag] = {"layer_sizes": z, "layers": layers}
+            for name, cfg_json in configs(z).items():
+                out_sizes[tag][name] = measure(cfg_json, z, name)
+    print(json.dumps({"metric": "prefill and decode tokens/s of the Dogilorn design beside Qwen3 with the same window at equal layer sizes (bf16, random weights)",
+                      "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": 3, "dtype": "bf16",
+                      "data": "synthetic: seeded random weights and random token ids",
+                      "config": {"layers": layers, "vocab": vocab, "prefill_tokens": T, "decode_context": ctx, "window": window, "keep_first": keep, "page_size": page,
+                                 "pattern": "attention with a dense feed-forward, attention with an expert mixture, attention on the keys and values of the layer before; repeated",
+                                 "timing": "CUDA events; inputs (weights and caches of 64 requests) exceed L2"},
+                      "peaks": {"hbm_gbs": hbm_gbs, "bf16_tflops": bf16_tflops, "source": peak_src}, "sizes": out_sizes, "clocks": clocks.summary()}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -718,9 +798,9 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1/64 and short-context points")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel rooflines")
-    ap.add_argument("--workload", default="decode", choices=["decode", "mixed", "nezolorn", "daronex", "naforax"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "mixed", "nezolorn", "daronex", "naforax", "dogilorn"],
                     help="decode: the contract's line (default); mixed: a continuous batch of --requests requests with prompts of 64 to 2,048 "
-                         "tokens and 128 generated tokens each through LLMEngine, its own line; nezolorn, daronex, naforax: prefill and decode of that design "
+                         "tokens and 128 generated tokens each through LLMEngine, its own line; nezolorn, daronex, naforax, dogilorn: prefill and decode of that design "
                          "beside Qwen3 at equal layer sizes, its own line")
     ap.add_argument("--requests", type=int, default=64, help="mixed workload: number of requests")
     ap.add_argument("--budget", type=int, default=2048, help="mixed workload: max_num_batched_tokens")
@@ -743,6 +823,8 @@ def main() -> int:
         return daronex_workload(args)
     if args.workload == "naforax":
         return naforax_workload(args)
+    if args.workload == "dogilorn":
+        return dogilorn_workload(args)
     hbm_gbs, bf16_tflops, bf16_sustained, peak_src = peaks()
     cfg_json = dict(QWEN3_8B)
     cfg_json.update(SHAPES[args.shape])
