@@ -179,6 +179,51 @@ __global__ void clamped_glu_kernel(const TI* __restrict__ gate_up, const float* 
     }
 }
 
+// The same, four neighbouring outputs a thread (inter, and with it every row pitch, a multiple of 4; arrays aligned for 4-element accesses).
+template <typename TI, typename TO>
+__global__ void clamped_glu_quads_kernel(const TI* __restrict__ gate_up, const float* __restrict__ bias, TO* __restrict__ out, int inter, long long quads,
+                                         float limit, float alpha)
+{
+    pdl_enter();
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    const int per_row = inter / 4;
+    for (; i < quads; i += stride) {
+        const long long row = i / per_row;
+        const int col = (int)(i - row * per_row) * 4;
+        const TI* src = gate_up + row * 2 * inter;
+        float g[4], u[4], o[4];
+        if constexpr (sizeof(TI) == 4) {
+            const float4 a = *reinterpret_cast<const float4*>(src + col), b = *reinterpret_cast<const float4*>(src + inter + col);
+            g[0] = a.x; g[1] = a.y; g[2] = a.z; g[3] = a.w; u[0] = b.x; u[1] = b.y; u[2] = b.z; u[3] = b.w;
+        } else {
+            const uint2 a = *reinterpret_cast<const uint2*>(src + col), b = *reinterpret_cast<const uint2*>(src + inter + col);
+            const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a);
+            const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&b);
+            g[0] = __low2float(a2[0]); g[1] = __high2float(a2[0]); g[2] = __low2float(a2[1]); g[3] = __high2float(a2[1]);
+            u[0] = __low2float(b2[0]); u[1] = __high2float(b2[0]); u[2] = __low2float(b2[1]); u[3] = __high2float(b2[1]);
+        }
+        if (bias != nullptr) {
+            const float4 bg = *reinterpret_cast<const float4*>(bias + col), bu = *reinterpret_cast<const float4*>(bias + inter + col);
+            g[0] += bg.x; g[1] += bg.y; g[2] += bg.z; g[3] += bg.w; u[0] += bu.x; u[1] += bu.y; u[2] += bu.z; u[3] += bu.w;
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float gg = fminf(g[e], limit), uu = fminf(fmaxf(u[e], -limit), limit);
+            o[e] = gg / (1.0f + expf(-alpha * gg)) * (uu + 1.0f);
+        }
+        if constexpr (sizeof(TO) == 4) {
+            *reinterpret_cast<float4*>(out + i * 4) = make_float4(o[0], o[1], o[2], o[3]);
+        } else {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(o[0], o[1]), hi = __floats2bfloat162_rn(o[2], o[3]);
+            uint2 x;
+            x.x = *reinterpret_cast<uint32_t*>(&lo);
+            x.y = *reinterpret_cast<uint32_t*>(&hi);
+            *reinterpret_cast<uint2*>(out + i * 4) = x;
+        }
+    }
+}
+
 extern "C" int spy_clamped_glu(const void* gate_up, int in_dtype, const float* bias, void* out, int out_dtype, int tokens, int inter, float limit,
                                float alpha, cudaStream_t stream)
 {
@@ -188,9 +233,18 @@ extern "C" int spy_clamped_glu(const void* gate_up, int in_dtype, const float* b
     long long blocks = (total + 255) / 256;
     const long long most = (long long)spy_sm_count() * 32;
     if (blocks > most) blocks = most;
+    const bool quads = inter % 4 == 0 && ((reinterpret_cast<uintptr_t>(gate_up) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(bias)) & 15) == 0;
+    if (quads) {
+        blocks = (total / 4 + 255) / 256;
+        if (blocks > most) blocks = most;
+    }
     SPY_DISPATCH_DTYPE(in_dtype, TI, {
         SPY_DISPATCH_DTYPE(out_dtype, TO, {
-            spy_launch(clamped_glu_kernel<TI, TO>, dim3((int)blocks), dim3(256), 0, stream, (const TI*)gate_up, bias, (TO*)out, inter, total, limit, alpha);
+            if (quads)
+                spy_launch(clamped_glu_quads_kernel<TI, TO>, dim3((int)blocks), dim3(256), 0, stream, (const TI*)gate_up, bias, (TO*)out, inter, total / 4, limit,
+                           alpha);
+            else
+                spy_launch(clamped_glu_kernel<TI, TO>, dim3((int)blocks), dim3(256), 0, stream, (const TI*)gate_up, bias, (TO*)out, inter, total, limit, alpha);
         })
     })
     SPY_CHECK_LAUNCH("clamped_glu");

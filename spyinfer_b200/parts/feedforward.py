@@ -127,7 +127,7 @@ class GatedMLP(FeedForward):
             return self.down(self.gate_up(x, epilogue="swiglu" if self.activation == "silu" else "geglu_tanh"), defer=self.defer_output)
         z = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
         if self.activation == "clamped_swish":
-            kernels.clamped_glu(self.gate_up(x, out_dtype=torch.float32), self.gate_up_bias, z, self.limit, self.slope)     # biases and clamps meet the unrounded products
+            kernels.clamped_glu(self.gate_up(x), self.gate_up_bias, z, self.limit, self.slope)     # the biases are added and the clamps applied in 32-bit
             return self.down(z, defer=self.defer_output)
         gu = self.gate_up(x)
         if self.has_bias:
