@@ -2,7 +2,9 @@
 //   v      = x[row] + scale_a * a_w * sum_s a[s][row] + scale_b * sum_s b[s][row]    32-bit sums, parts in their order
 //   x[row] = v                                             when write_back (the residual stream)
 //   out    = (v - mean(v)) / sqrt(mean((v - mean(v))^2) + eps) * w (+ bias)          32-bit statistics, two passes
-// a_w (null, or [len] of the weight's type) multiplies the first result element by element along the row (a layer scale).
+// a_w (null, or [len] of the weight's type) multiplies the first result element by element along the row (a layer scale);
+// a_bias (null, or [len] float32) is added to the first result ahead of that: x += scale_a * a_w * (sum_s a[s] + a_bias), the
+// bias of the projection that made the result.
 // a and b are null, one array [*, len], or stacks of split-K partial products (splits arrays, split_stride elements
 // apart); two of them because a layer whose mixer is two mixers side by side hands over two results with a weight each.
 // With center == 0 the mean is not removed (an RMS norm with the same fused sums).
@@ -41,7 +43,7 @@ template <typename TX, typename TD, typename TW, typename TO, bool VEC>
 __global__ void __launch_bounds__(1024)
 layernorm_kernel(TX* x, const TD* __restrict__ a, int a_splits, long long a_stride, float a_scale, const TD* __restrict__ b, int b_splits,
                  long long b_stride, float b_scale, const int* __restrict__ rows, const TW* __restrict__ w, TO* __restrict__ out, int len, float eps,
-                 int write_back, int center, const TW* __restrict__ bias, const TW* __restrict__ a_w)
+                 int write_back, int center, const TW* __restrict__ bias, const TW* __restrict__ a_w, const float* __restrict__ a_bias)
 {
     extern __shared__ __align__(16) float row_buf[];  // len floats, then 33 of scratch
     pdl_enter();
@@ -63,6 +65,12 @@ layernorm_kernel(TX* x, const TD* __restrict__ a, int a_splits, long long a_stri
                 if constexpr (VEC) Quad<TD>::load(ar + (size_t)s * a_stride + i, p); else p[0] = to_f32(ar[(size_t)s * a_stride + i]);
 #pragma unroll
                 for (int e = 0; e < E; ++e) d[e] += p[e];
+            }
+            if (a_bias) {
+                float ab[4];
+                if constexpr (VEC) Quad<float>::load(a_bias + i, ab); else ab[0] = a_bias[i];
+#pragma unroll
+                for (int e = 0; e < E; ++e) d[e] += ab[e];
             }
             if (a_w) {
                 float aw[4];
@@ -123,7 +131,7 @@ layernorm_kernel(TX* x, const TD* __restrict__ a, int a_splits, long long a_stri
 // out: [n, len] of out_dtype.  write_back stores the sum into x and needs rows == null.  bias, a_w: null or [len] of w_dtype.
 static int run_layernorm(void* x, int x_dtype, const void* a, int a_splits, long long a_stride, float a_scale, const void* b, int b_splits,
                          long long b_stride, float b_scale, int delta_dtype, const int* rows, const void* w, int w_dtype, void* out, int out_dtype,
-                         int n, int len, float eps, int write_back, int center, const void* bias, const void* a_w, cudaStream_t stream)
+                         int n, int len, float eps, int write_back, int center, const void* bias, const void* a_w, const float* a_bias, cudaStream_t stream)
 {
     if (n <= 0) return 0;
     if (len <= 0) SPY_FAIL("layernorm: row length %d must be positive", len);
@@ -135,7 +143,7 @@ static int run_layernorm(void* x, int x_dtype, const void* a, int a_splits, long
     if (smem > 227 * 1024) SPY_FAIL("layernorm: a row of %d elements does not fit in shared memory (limit %d)", len, (227 * 1024) / 4 - 33);
     const bool vec = len % 4 == 0 && a_stride % 4 == 0 && b_stride % 4 == 0 &&
                      ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(w) |
-                       reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(bias) | reinterpret_cast<uintptr_t>(a_w)) & 15) == 0;
+                       reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(bias) | reinterpret_cast<uintptr_t>(a_w) | reinterpret_cast<uintptr_t>(a_bias)) & 15) == 0;
     // many rows: fewer threads a row (two quads each) and so more rows an SM at a time; few rows: the row spread as wide as it goes
     int threads = (len / (vec ? (n >= 512 ? 8 : 4) : 4) + 31) / 32 * 32;
     threads = threads < 64 ? 64 : (threads > 1024 ? 1024 : threads);
@@ -146,7 +154,7 @@ static int run_layernorm(void* x, int x_dtype, const void* a, int a_splits, long
                     auto kernel = vec ? layernorm_kernel<TX, TD, TW, TO, true> : layernorm_kernel<TX, TD, TW, TO, false>;
                     if (smem > 48 * 1024) SPY_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
                     spy_launch(kernel, dim3(n), dim3(threads), smem, stream, (TX*)x, (const TD*)a, a_splits, a_stride, a_scale, (const TD*)b, b_splits,
-                               b_stride, b_scale, rows, (const TW*)w, (TO*)out, len, eps, write_back, center, (const TW*)bias, (const TW*)a_w);
+                               b_stride, b_scale, rows, (const TW*)w, (TO*)out, len, eps, write_back, center, (const TW*)bias, (const TW*)a_w, a_bias);
                 })
             })
         })
@@ -160,17 +168,18 @@ extern "C" int spy_layernorm(void* x, int x_dtype, const void* a, int a_splits, 
                              int n, int len, float eps, int write_back, int center, cudaStream_t stream)
 {
     return run_layernorm(x, x_dtype, a, a_splits, a_stride, a_scale, b, b_splits, b_stride, b_scale, delta_dtype, rows, w, w_dtype, out, out_dtype, n, len,
-                         eps, write_back, center, nullptr, nullptr, stream);
+                         eps, write_back, center, nullptr, nullptr, nullptr, stream);
 }
 
-// The same with a bias behind the weight and a per-channel multiplier of the first result (each null or [len] of w_dtype).
-extern "C" int spy_layernorm_affine(void* x, int x_dtype, const void* a, int a_splits, long long a_stride, float a_scale, const void* a_w, const void* b,
+// The same with a bias behind the weight and a per-channel multiplier of the first result (each null or [len] of w_dtype), and a
+// bias of the first result itself (null or [len] float32).
+extern "C" int spy_layernorm_affine(void* x, int x_dtype, const void* a, int a_splits, long long a_stride, float a_scale, const void* a_w, const float* a_bias, const void* b,
                                     int b_splits, long long b_stride, float b_scale, int delta_dtype, const int* rows, const void* w, const void* bias,
                                     int w_dtype, void* out, int out_dtype, int n, int len, float eps, int write_back, int center, cudaStream_t stream)
 {
-    if (a_w != nullptr && a == nullptr) SPY_FAIL("layernorm: a per-channel multiplier without a result to multiply");
+    if ((a_w != nullptr || a_bias != nullptr) && a == nullptr) SPY_FAIL("layernorm: a per-channel multiplier or a bias without a result to go with");
     return run_layernorm(x, x_dtype, a, a_splits, a_stride, a_scale, b, b_splits, b_stride, b_scale, delta_dtype, rows, w, w_dtype, out, out_dtype, n, len,
-                         eps, write_back, center, bias, a_w, stream);
+                         eps, write_back, center, bias, a_w, a_bias, stream);
 }
 
 // out = scale_a * sum_s a[s] + scale_b * sum_s b[s], element by element in 32-bit: the weighted sum of two results (each

@@ -47,10 +47,12 @@ class ScaledParts:
 class ChannelScaled:
     """A sublayer output that the stream takes multiplied element by element along the row: ``residual += y * weight``
     with ``weight [size]`` (a layer scale).  ``y`` is ``[rows, size]`` or a stack ``[splits, rows, size]`` of float32 partial
-    products.  A norm that says ``takes_channel_scale`` forms the product in its own kernel."""
+    products.  ``bias`` (optional, float32 ``[size]``): the bias of the projection that made ``y``, still to be added:
+    ``residual += (y + bias) * weight``.  A norm that says ``takes_channel_scale`` forms the product in its own kernel."""
 
     y: torch.Tensor
     weight: torch.Tensor
+    bias: Optional[torch.Tensor] = None
 
 
 @dataclass
@@ -146,6 +148,10 @@ class Mixer(Part):
 
 class FeedForward(Part):
     defer_output: bool = True     # as ``Mixer.defer_output``
+    #: set by a block arrangement whose next norm adds a projection's bias itself: a feed-forward whose last projection has a
+    #: bias then leaves it out and offers it as ``output_bias`` (float32 ``[size]``, None when there is none)
+    leave_output_bias: bool = False
+    output_bias: Optional[torch.Tensor] = None
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError

@@ -116,6 +116,8 @@ class ScaledPreNormBlock(Block):
         if hasattr(self.mixer, "scaled_parts_ok"):
             self.mixer.scaled_parts_ok = self.ffn_norm is not None and self.mixer_scale is None      # the sum is formed by this layer's second norm
         self._conv_state = self.mixer_conv is not None and self.mixer_conv.cache_need() is not None
+        if self.ffn_scale is not None:
+            self.feed_forward.leave_output_bias = True       # the norm that applies the scale adds the last projection's bias too
 
     def cache_need(self):
         from ..config.spec import CompositeCacheNeed
@@ -143,7 +145,7 @@ class ScaledPreNormBlock(Block):
             return hidden, a
         x = self.ffn_norm.forward_add(hidden, a, scale=self.residual_scale)
         f = self.feed_forward.forward(x)
-        return hidden, self.ffn_scale.defer(f) if self.ffn_scale is not None else f
+        return hidden, self.ffn_scale.defer(f, self.feed_forward.output_bias) if self.ffn_scale is not None else f
 
 
 @register_block("sandwich_norm")

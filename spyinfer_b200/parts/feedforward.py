@@ -113,7 +113,10 @@ class GatedMLP(FeedForward):
         if self.has_bias:
             # the gate and up biases are added by the activation's kernel (32-bit), the down bias by a pass behind its product
             self.gate_up_bias = torch.cat([tensors[p + n["gate"] + ".b"].float(), tensors[p + n["up"] + ".b"].float()]).contiguous()
-        self.down = Linear(tensors[p + n["down"]], self.ctx.dtype, bias=tensors[p + n["down"] + ".b"].float().contiguous() if self.has_bias else None)
+        down_bias = tensors[p + n["down"] + ".b"].float().contiguous() if self.has_bias else None
+        if self.leave_output_bias:           # the consumer adds it (and may then take the down product's split-K parts unsummed)
+            self.output_bias, down_bias = down_bias, None
+        self.down = Linear(tensors[p + n["down"]], self.ctx.dtype, bias=down_bias)
         self.gate_up.hint_next = not self.fused       # fused: the down product follows at once
 
     def linears(self):
