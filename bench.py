@@ -759,7 +759,7 @@ def dogilorn_workload(args) -> int:
                     rate(block, "sink_attention.spy_sink_qkv_store",
                          nbytes=float(rows) * (layers * H * hd * 6 + n_own * 2 * z["kv"] * hd * 6))
                     rate(block, "sink_attention.spy_sink_merge", nbytes=float(layers) * rows * H * hd * (2 + 2 + 2))
-                    rate(block, "swiglu.spy_clamped_glu", nbytes=float(n_dense) * rows * z["ff"] * (8 + 2))
+                    rate(block, "swiglu.spy_clamped_glu", nbytes=float(n_dense) * rows * z["ff"] * (4 + 2))
                     cols = z["experts"] * z["expert_ff"] + z["shared_ff"]
                     rate(block, "moe.spy_moe_activation_routed", nbytes=float(n_moe) * rows * ((z["top"] * z["expert_ff"] + z["shared_ff"]) * 4 + cols * 2))
                 else:
