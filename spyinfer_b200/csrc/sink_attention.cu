@@ -344,78 +344,50 @@ template <int V>
 __global__ void sink_merge_rows_kernel(const bf16* __restrict__ q, long long q_ld, bf16* __restrict__ out, const float* __restrict__ lse,
                                        const bf16* __restrict__ pages, const int* __restrict__ block_table, int table_width, int page_size, int num_pages,
                                        int nh, int nkv, const int* __restrict__ positions, const int* __restrict__ seq_of_token, int tokens,
-                                       int window, int keep_first, int sink, float scale, int* status)
+                                       int window, int keep_first, int sink, float scale, int* status, int group)
 {
-    // One warp a (token, key/value head): the kept keys' rows are fetched once (the first four stay in registers) and serve the
-    // group's query heads one after the other, the next head's query, result and logarithm being requested while one is merged.
     constexpr int HD = 32 * V, KB = 4;
     pdl_enter();
+    // grid: x = token, y = groups of the block's warps over the heads; a warp a (token, head); no division on the way
     const int lane = threadIdx.x & 31;
-    const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (item >= (long long)tokens * nkv) return;
-    const int t = (int)(item / nkv), kvh = (int)(item - (long long)t * nkv), G = nh / nkv;
-    const int pos = positions[t];
+    const int t = blockIdx.x, h = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (h >= nh) return;
+    const int pos = positions[t], kvh = h / group;
     const int kept = min(keep_first, spy_first_key(pos, window));
     if (kept <= 0 && !sink) return;
-    const int* bt = block_table + (long long)seq_of_token[t] * table_width;
-    float kv0[KB][V], vv0[KB][V];
-    bool ok0[KB];
-    const auto fetch = [&](int j, float (&kr)[V], float (&vr)[V]) -> bool {
-        const int lp = j / page_size;
-        const int page = (j < kept && lp < table_width) ? bt[lp] : -1;
-        const bool ok = page >= 0 && page < num_pages;
-        if (j < kept && !ok && lane == 0) report_status(status, SPY_STATUS_BAD_PAGE, t);
-        if (ok) {
-            const bf16* k = pages + ((((long long)page * 2) * nkv + kvh) * page_size + j % page_size) * HD + lane * V;
-            load_lane<V>(k, kr);
-            load_lane<V>(k + (long long)nkv * page_size * HD, vr);
-        }
-        return ok;
-    };
+    bf16* orow = out + ((long long)t * nh + h) * HD + lane * V;
+    const float lw = lse[(long long)t * nh + h];
+    float ov[V], acc[V];
+    load_lane<V>(orow, ov);
 #pragma unroll
-    for (int b = 0; b < KB; ++b) ok0[b] = fetch(b, kv0[b], vv0[b]);
-    const int h0 = kvh * G;
-    const bf16* qr = q + (long long)t * q_ld + (long long)h0 * HD + lane * V;
-    bf16* orow = out + ((long long)t * nh + h0) * HD + lane * V;
-    const float* lrow = lse + (long long)t * nh + h0;
-    float qn[V], on[V], ln = lrow[0];
-    load_lane<V>(qr, qn);
-    load_lane<V>(orow, on);
-    for (int n = 0; n < G; ++n) {
-        float qv[V], ov[V], acc[V];
-        const float lw = ln;
-#pragma unroll
-        for (int i = 0; i < V; ++i) {
-            qv[i] = qn[i];
-            ov[i] = on[i];
-            acc[i] = 0.f;
-        }
-        if (n + 1 < G) {                         // the next head's inputs are on their way while this one is merged
-            load_lane<V>(qr + (long long)(n + 1) * HD, qn);
-            load_lane<V>(orow + (long long)(n + 1) * HD, on);
-            ln = lrow[n + 1];
-        }
-        float m_run = sink ? fmaxf(lw, 0.f) : lw, d_extra = 0.f;
+    for (int i = 0; i < V; ++i) acc[i] = 0.f;
+    float m_run = sink ? fmaxf(lw, 0.f) : lw, d_extra = 0.f;
+    if (kept > 0) {
+        const int* bt = block_table + (long long)seq_of_token[t] * table_width;
+        float qv[V];
+        load_lane<V>(q + (long long)t * q_ld + (long long)h * HD + lane * V, qv);
+        int lp = 0, slot = 0;                                  // the page and the place in it of key j0 + b, stepped along
         for (int j0 = 0; j0 < kept; j0 += KB) {
             float dot[KB], vv[KB][V];
             bool ok[KB];
 #pragma unroll
             for (int b = 0; b < KB; ++b) {
-                float kv[V];
-                if (j0 == 0) {
-                    ok[b] = ok0[b];
-#pragma unroll
-                    for (int i = 0; i < V; ++i) {
-                        kv[i] = kv0[b][i];
-                        vv[b][i] = vv0[b][i];
-                    }
-                } else {
-                    ok[b] = fetch(j0 + b, kv, vv[b]);
-                }
+                const int j = j0 + b;
+                const int page = (j < kept && lp < table_width) ? bt[lp] : -1;
+                ok[b] = page >= 0 && page < num_pages;
                 dot[b] = 0.f;
+                if (j < kept && !ok[b] && lane == 0) report_status(status, SPY_STATUS_BAD_PAGE, t);
                 if (ok[b]) {
+                    const bf16* kr = pages + ((((long long)page * 2) * nkv + kvh) * page_size + slot) * HD + lane * V;
+                    float kv[V];
+                    load_lane<V>(kr, kv);
+                    load_lane<V>(kr + (long long)nkv * page_size * HD, vv[b]);
 #pragma unroll
                     for (int i = 0; i < V; ++i) dot[b] = fmaf(qv[i], kv[i], dot[b]);
+                }
+                if (++slot == page_size) {
+                    slot = 0;
+                    ++lp;
                 }
             }
 #pragma unroll
@@ -425,21 +397,21 @@ __global__ void sink_merge_rows_kernel(const bf16* __restrict__ q, long long q_l
 #pragma unroll
             for (int b = 0; b < KB; ++b) {
                 if (!ok[b]) continue;
-                const float sc = dot[b] * scale, m_new = fmaxf(m_run, sc);
-                const float alpha = m_run == -INFINITY ? 0.f : expf(m_run - m_new), pw = expf(sc - m_new);
-                d_extra = d_extra * alpha + pw;
+                const float s = dot[b] * scale, m_new = fmaxf(m_run, s);
+                const float alpha = m_run == -INFINITY ? 0.f : expf(m_run - m_new), p = expf(s - m_new);
+                d_extra = d_extra * alpha + p;
 #pragma unroll
-                for (int i = 0; i < V; ++i) acc[i] = fmaf(pw, vv[b][i], acc[i] * alpha);
+                for (int i = 0; i < V; ++i) acc[i] = fmaf(p, vv[b][i], acc[i] * alpha);
                 m_run = m_new;
             }
         }
-        const float ww = lw == -INFINITY ? 0.f : expf(lw - m_run);
-        const float denom = ww + d_extra + (sink ? expf(-m_run) : 0.f);
-        const float inv = denom > 0.f ? 1.0f / denom : 0.f;
-#pragma unroll
-        for (int i = 0; i < V; ++i) ov[i] = (ov[i] * ww + acc[i]) * inv;
-        store_lane<V>(orow + (long long)n * HD, ov);
     }
+    const float ww = lw == -INFINITY ? 0.f : expf(lw - m_run);
+    const float denom = ww + d_extra + (sink ? expf(-m_run) : 0.f);
+    const float inv = denom > 0.f ? 1.0f / denom : 0.f;
+#pragma unroll
+    for (int i = 0; i < V; ++i) ov[i] = (ov[i] * ww + acc[i]) * inv;
+    store_lane<V>(orow, ov);
 }
 
 // q [T, q_ld] (heads * hd columns read), out [T, nh * hd] rewritten in place, lse [T, nh] float32, pages as above.
@@ -455,14 +427,15 @@ extern "C" int spy_sink_merge(const void* q, long long q_ld, void* out, int act_
     const int warps = 8;
     const bool aligned = ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(pages)) & 7) == 0 && q_ld % 4 == 0;
     if (act_dtype == SPY_BF16 && aligned && (hd == 128 || hd == 64)) {
-        const long long groups = (long long)tokens * nkv;
-        const dim3 grid((unsigned)((groups + warps - 1) / warps)), block(warps * 32);
+        const int per_block = nh < warps ? nh : warps;
+        if ((nh + per_block - 1) / per_block > 65535) SPY_FAIL("sink_merge: %d heads exceed the grid", nh);
+        const dim3 grid((unsigned)tokens, (unsigned)((nh + per_block - 1) / per_block)), block(per_block * 32);
         if (hd == 128)
             spy_launch(sink_merge_rows_kernel<4>, grid, block, 0, stream, (const bf16*)q, q_ld, (bf16*)out, lse, (const bf16*)pages, block_table, table_width,
-                       page_size, num_pages, nh, nkv, positions, seq_of_token, tokens, window, keep_first, sink, scale, status);
+                       page_size, num_pages, nh, nkv, positions, seq_of_token, tokens, window, keep_first, sink, scale, status, nh / nkv);
         else
             spy_launch(sink_merge_rows_kernel<2>, grid, block, 0, stream, (const bf16*)q, q_ld, (bf16*)out, lse, (const bf16*)pages, block_table, table_width,
-                       page_size, num_pages, nh, nkv, positions, seq_of_token, tokens, window, keep_first, sink, scale, status);
+                       page_size, num_pages, nh, nkv, positions, seq_of_token, tokens, window, keep_first, sink, scale, status, nh / nkv);
         SPY_CHECK_LAUNCH("sink_merge");
         return 0;
     }
