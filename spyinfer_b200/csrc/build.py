@@ -30,7 +30,7 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr", "-Xc
               "-Xcompiler", "-fvisibility=default"]
 HOST_MODULES = ["engine_core"]                 # plain C++, built with the host compiler
 HOST_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=default"]
-MODULES = ["embedding", "rmsnorm", "residual_norm", "layernorm", "group_norm", "time_conv", "diff_attention", "gated_scan", "moe", "attention_pool", "recurrence", "qk_rope_store", "latent", "attention_generic", "attention_mma", "attention_tc", "attention_decode", "gemm_simt", "gemm_tcgen05", "swiglu", "sampling"]
+MODULES = ["embedding", "rmsnorm", "residual_norm", "layernorm", "group_norm", "time_conv", "diff_attention", "gated_scan", "moe", "sink_attention", "attention_pool", "recurrence", "qk_rope_store", "latent", "attention_generic", "attention_mma", "attention_tc", "attention_decode", "gemm_simt", "gemm_tcgen05", "swiglu", "sampling"]
 
 _loaded: Dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()

@@ -62,22 +62,31 @@ __global__ void time_conv_kernel(const TI* __restrict__ in, long long ld_in, con
         for (int i = 0; i < MAXT - 1; ++i)
             if (i < hist_n) hist[i] = to_f32(in[(long long)(t0 - hist_n + i) * ld_in + c]);
     }
-    for (int t = t0; t < t1; ++t) {
-        const float x = to_f32(in[(long long)t * ld_in + c]);
-        float acc = b;
+    // four tokens' inputs are requested together, then used in order
+    for (int tb = t0; tb < t1; tb += 4) {
+        float xs[4];
 #pragma unroll
-        for (int i = 0; i < MAXT - 1; ++i)
-            if (i < hist_n) acc = fmaf(k[i], hist[i], acc);
+        for (int u = 0; u < 4; ++u) xs[u] = tb + u < t1 ? to_f32(in[(long long)(tb + u) * ld_in + c]) : 0.f;
 #pragma unroll
-        for (int j = 0; j < MAXT; ++j)
-            if (j == hist_n) acc = fmaf(k[j], x, acc);
-        if (residual) acc += x;
-        if (act == 1) acc = acc / (1.0f + expf(-acc));
-        out[(long long)t * ld_out + c] = from_f32<TO>(acc);
+        for (int u = 0; u < 4; ++u) {
+            const int t = tb + u;
+            if (t >= t1) break;
+            const float x = xs[u];
+            float acc = b;
 #pragma unroll
-        for (int i = 0; i < MAXT - 1; ++i) {
-            if (i + 1 < hist_n) hist[i] = hist[i + 1];
-            else if (i + 1 == hist_n) hist[i] = x;
+            for (int i = 0; i < MAXT - 1; ++i)
+                if (i < hist_n) acc = fmaf(k[i], hist[i], acc);
+#pragma unroll
+            for (int j = 0; j < MAXT; ++j)
+                if (j == hist_n) acc = fmaf(k[j], x, acc);
+            if (residual) acc += x;
+            if (act == 1) acc = acc / (1.0f + expf(-acc));
+            out[(long long)t * ld_out + c] = from_f32<TO>(acc);
+#pragma unroll
+            for (int i = 0; i < MAXT - 1; ++i) {
+                if (i + 1 < hist_n) hist[i] = hist[i + 1];
+                else if (i + 1 == hist_n) hist[i] = x;
+            }
         }
     }
 }
