@@ -14,7 +14,7 @@
 
 SPY_MODULE(spy_time_conv)
 
-constexpr int TC_PIECE = 32;       // tokens a thread walks; at least taps - 1, so that only a run's first piece needs the state
+constexpr int TC_PIECE = 16;       // tokens a thread walks; at least taps - 1, so that only a run's first piece needs the state
 
 template <int MAXT, typename TI, typename TK, typename TO>
 __global__ void time_conv_kernel(const TI* __restrict__ in, long long ld_in, const TK* __restrict__ kernel, const TK* __restrict__ bias,

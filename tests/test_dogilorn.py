@@ -48,7 +48,9 @@ def _dense(ff, limit):
 # convolution, sixteen query heads on one key/value head, kept tokens that fill a page, a reader without kept tokens, a layer
 # without a feed-forward.  d: more than sixteen query heads a key/value head and an odd head size (the plain attention
 # kernel on both paths), more kept tokens than the window is wide, five taps, every expert chosen.  e: one tap (no state), a
-# window of one token, a reader that sees every key of a layer whose own window is one.
+# window of one token, a reader that sees every key of a layer whose own window is one.  f: a width that is no multiple of 8 (the
+# CUDA-core products on both paths), sixteen taps, an odd number of rotated pairs, a reader with more query heads than the layer it
+# reads, one group kept, a head wider than the tensor-core attention takes (values wider than keys).
 DG = {
     "a": dict(seed=31, config={
         "architecture": "Dogilorn", "vocab": 211, "width": 64, "norm": {"eps": 1e-5}, "canon": {"taps": 3}, "embedding": {"scale": 2.5},
@@ -77,6 +79,13 @@ DG = {
         "architecture": "Dogilorn", "vocab": 97, "width": 48, "norm": {"eps": 1e-5}, "canon": {"taps": 5}, "embedding": {"scale": 0.5},
         "layers": [
             {"type": "attention", "mixer": _attn(20, 1, 7, 5, 0.4, mask=(25, 30), rot=(100.0, 4)), "mlp": _moe(4, 0, 4, 12, shared=8)},
+        ]}),
+    "f": dict(seed=36, config={
+        "architecture": "Dogilorn", "vocab": 83, "width": 100, "norm": {"eps": 1e-5}, "canon": {"taps": 16}, "embedding": {"scale": 1.5},
+        "layers": [
+            {"type": "attention", "mixer": _attn(6, 3, 40, 36, 0.16, mask=(50, 12), rot=(2000.0, 10)), "mlp": _moe(7, 1, 2, 20, groups=(4, 1))},
+            {"type": "attention", "mixer": _attn(12, 3, 40, 36, 0.2, mask=(18, 20), rot=(2000.0, 10), kv_from=0), "mlp": _dense(72, 1.2)},
+            {"type": "attention", "mixer": _attn(2, 1, 160, 192, 0.08, mask=(31, 2), rot=(100.0, 160)), "mlp": None},
         ]}),
     "e": dict(seed=35, config={
         "architecture": "Dogilorn", "vocab": 131, "width": 80, "norm": {"eps": 1e-6}, "canon": {"taps": 1},
