@@ -73,38 +73,55 @@ gemm_simt_kernel(const TA* __restrict__ A, long long lda, const TW* __restrict__
 // under way at once, and the threads' sums are added in a fixed order.  A row's result does not depend on M either.
 constexpr int SKINNY_N = 32, SKINNY_NG = 16, SKINNY_THREADS = 128;
 
-template <typename TA, typename TW, typename TC>
+// ROWS rows of A a block: with many rows every weight element a block fetches serves ROWS of them (each block reads all of W, so
+// with one row a block the weights cross the L2 once a row).  A row's sums are formed in the same order whatever ROWS is.
+template <typename TA, typename TW, typename TC, int ROWS>
 __global__ void __launch_bounds__(SKINNY_THREADS)
 gemm_skinny_kernel(const TA* __restrict__ A, long long lda, const TW* __restrict__ W, long long ldw, TC* __restrict__ C, long long ldc,
                    int M, int N, int K)
 {
-    __shared__ float part[SKINNY_THREADS / 32][SKINNY_NG];
+    __shared__ float part[ROWS][SKINNY_THREADS / 32][SKINNY_NG];
     pdl_enter();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const long long m = blockIdx.x;
-    const TA* a = A + m * lda;
-    for (int n0 = 0; n0 < N; n0 += SKINNY_NG) {
-        float acc[SKINNY_NG];
+    const long long m0 = (long long)blockIdx.x * ROWS;
+    const TA* a[ROWS];
 #pragma unroll
-        for (int j = 0; j < SKINNY_NG; ++j) acc[j] = 0.f;
+    for (int r = 0; r < ROWS; ++r) a[r] = A + (m0 + r < M ? m0 + r : m0) * lda;      // rows beyond the last: the first again, never stored
+    for (int n0 = 0; n0 < N; n0 += SKINNY_NG) {
+        float acc[ROWS][SKINNY_NG];
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r)
+#pragma unroll
+            for (int j = 0; j < SKINNY_NG; ++j) acc[r][j] = 0.f;
 #pragma unroll 2
         for (int k = threadIdx.x; k < K; k += SKINNY_THREADS) {
-            const float av = to_f32(a[k]);
+            float av[ROWS];
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r) av[r] = to_f32(a[r][k]);
 #pragma unroll
             for (int j = 0; j < SKINNY_NG; ++j)
-                if (n0 + j < N) acc[j] = fmaf(av, to_f32(W[(size_t)(n0 + j) * ldw + k]), acc[j]);
+                if (n0 + j < N) {
+                    const float w = to_f32(W[(size_t)(n0 + j) * ldw + k]);
+#pragma unroll
+                    for (int r = 0; r < ROWS; ++r) acc[r][j] = fmaf(av[r], w, acc[r][j]);
+                }
         }
 #pragma unroll
-        for (int j = 0; j < SKINNY_NG; ++j) {
-            const float sum = warp_sum(acc[j]);
-            if (lane == 0) part[warp][j] = sum;
-        }
+        for (int r = 0; r < ROWS; ++r)
+#pragma unroll
+            for (int j = 0; j < SKINNY_NG; ++j) {
+                const float sum = warp_sum(acc[r][j]);
+                if (lane == 0) part[r][warp][j] = sum;
+            }
         __syncthreads();
-        if (threadIdx.x < SKINNY_NG && n0 + threadIdx.x < N) {
-            float sum = 0.f;
+        for (int i = threadIdx.x; i < ROWS * SKINNY_NG; i += SKINNY_THREADS) {
+            const int r = i / SKINNY_NG, j = i % SKINNY_NG;
+            if (m0 + r < M && n0 + j < N) {
+                float sum = 0.f;
 #pragma unroll
-            for (int w = 0; w < SKINNY_THREADS / 32; ++w) sum += part[w][threadIdx.x];
-            C[m * ldc + n0 + threadIdx.x] = from_f32<TC>(sum);
+                for (int w = 0; w < SKINNY_THREADS / 32; ++w) sum += part[r][w][j];
+                C[(m0 + r) * ldc + n0 + j] = from_f32<TC>(sum);
+            }
         }
         __syncthreads();
     }
@@ -120,8 +137,12 @@ extern "C" int spy_gemm_simt(const void* A, int a_dtype, long long lda, const vo
         SPY_DISPATCH_DTYPE(a_dtype, TA, {
             SPY_DISPATCH_DTYPE(w_dtype, TW, {
                 SPY_DISPATCH_DTYPE(c_dtype, TC, {
-                    spy_launch(gemm_skinny_kernel<TA, TW, TC>, dim3((unsigned)M), dim3(SKINNY_THREADS), 0, stream, (const TA*)A, lda,
-                               (const TW*)W, ldw, (TC*)C, ldc, M, N, K);
+                    if (M >= 1024)
+                        spy_launch(gemm_skinny_kernel<TA, TW, TC, 4>, dim3((unsigned)((M + 3) / 4)), dim3(SKINNY_THREADS), 0, stream, (const TA*)A, lda,
+                                   (const TW*)W, ldw, (TC*)C, ldc, M, N, K);
+                    else
+                        spy_launch(gemm_skinny_kernel<TA, TW, TC, 1>, dim3((unsigned)M), dim3(SKINNY_THREADS), 0, stream, (const TA*)A, lda,
+                                   (const TW*)W, ldw, (TC*)C, ldc, M, N, K);
                 })
             })
         })
