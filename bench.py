@@ -728,7 +728,7 @@ def dogilorn_workload(args) -> int:
 
         def layer(i):
             mixer = {"heads": z["heads"], "kv_heads": z["kv"], "dim": z["hd"], "vdim": z["hd"], "scale": z["hd"] ** -0.5,
-                     "mask": {"size": window, "keep_first": keep}, "rot": {"base": 500000.0, "dims": 64}}
+                     "mask": {"size": window, "keep_first": keep}, "rot": {"base": 1000000.0, "dims": 64}}
             if i % 3 == 2:
                 mixer["kv_from"] = i - 1
             return {"type": "attention", "mixer": mixer, "mlp": dense if i % 2 == 0 else moe}
