@@ -113,9 +113,24 @@ __device__ __forceinline__ float gelu_tanh_mul(float g, float u)
     asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.7978845608028654f * fmaf(0.044715f * g, g * g, g)));
     return 0.5f * g * (1.0f + t) * u;
 }
-// EPI 1 and 3 are the gated epilogues: act(gate) * up over alternating rows
-__host__ __device__ constexpr bool gated_epilogue(int epi) { return epi == 1 || epi == 3; }
-template <int EPI> __device__ __forceinline__ float gated_mul(float g, float u) { return EPI == 3 ? gelu_tanh_mul(g, u) : silu_mul(g, u); }
+// What the clamped gated epilogue (EPI == 4) needs beside the product: the bias of the weight's rows as they lie (gate and up rows
+// alternating; null: none), the clamp and the slope:  g = min(gate + b, limit), u = clamp(up + b, -limit, limit), g * sigmoid(slope g) * (u + 1).
+struct GluArgs {
+    const float* bias;
+    float limit, slope;
+};
+__device__ __forceinline__ float clamped_swish_mul(float g, float u, const GluArgs& a)
+{
+    g = fminf(g, a.limit);
+    u = fminf(fmaxf(u, -a.limit), a.limit);
+    return __fdividef(g, 1.0f + __expf(-a.slope * g)) * (u + 1.0f);
+}
+// EPI 1, 3 and 4 are the gated epilogues: act(gate) * up over alternating rows
+__host__ __device__ constexpr bool gated_epilogue(int epi) { return epi == 1 || epi == 3 || epi == 4; }
+template <int EPI> __device__ __forceinline__ float gated_mul(float g, float u, const GluArgs& a)
+{
+    return EPI == 4 ? clamped_swish_mul(g, u, a) : (EPI == 3 ? gelu_tanh_mul(g, u) : silu_mul(g, u));
+}
 // the square of relu: the activation of a feed-forward without a gate (EPI == 2)
 __device__ __forceinline__ float relu_squared(float v) { const float p = fmaxf(v, 0.f); return p * p; }
 
@@ -128,7 +143,7 @@ template <int BN, typename TC, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 2)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y, TC* __restrict__ out,
                     long long ld, long long split_stride, int x_rows, int y_rows, int k_blocks, int k_blocks_per_split, int tile_rows,
-                    int* status, const uint8_t* __restrict__ next_weights, long long next_bytes)
+                    int* status, const uint8_t* __restrict__ next_weights, long long next_bytes, GluArgs glu)
 {
     using T = Tile<BN>;
     extern __shared__ uint8_t smem_raw[];
@@ -268,12 +283,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                     // weight tiles that the next product's blocks on this SM have already asked for.
                     const bool odd = (lane & 1) != 0;
                     bf16* staged = reinterpret_cast<bf16*>(tiles);
+                    const float row_bias = (EPI == 4 && glu.bias != nullptr && x < x_rows) ? glu.bias[x] : 0.f;   // this lane's weight row
 #pragma unroll
                     for (int j = 0; j < 32; j += 2) {
                         if (j < cols) {
-                            const float a = __uint_as_float(r[j]), b = __uint_as_float(r[j + 1]);
+                            const float a = __uint_as_float(r[j]) + row_bias, b = __uint_as_float(r[j + 1]) + row_bias;
                             const float got = __shfl_xor_sync(0xffffffffu, odd ? a : b, 1);
-                            const float v = gated_mul<EPI>(odd ? got : a, odd ? b : got);
+                            const float v = gated_mul<EPI>(odd ? got : a, odd ? b : got, glu);
                             staged[(c + j + (odd ? 1 : 0)) * SWIGLU_STAGE_LD + ((quarter * 32 + lane) >> 1)] = __float2bfloat16_rn(v);
                         }
                     }
@@ -371,13 +387,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 
 // Stores 32 consecutive accumulator columns of row x (normal mode), with the optional SwiGLU.
 template <typename TC, int EPI>
-__device__ __forceinline__ void store_chunk_normal(TC* base, long long ld, int x, int y, int x_rows, int y_rows, const uint32_t (&r)[32])
+__device__ __forceinline__ void store_chunk_normal(TC* base, long long ld, int x, int y, int x_rows, int y_rows, const uint32_t (&r)[32],
+                                                   const GluArgs& glu)
 {
     if (x >= x_rows || y >= y_rows) return;
     if constexpr (gated_epilogue(EPI)) {
         uint32_t o[16];
+        if (EPI == 4 && glu.bias != nullptr) {
+            // the columns y .. y + 31 are weight rows (gate and up in turns); every thread of the warp reads the same 32 biases
 #pragma unroll
-        for (int j = 0; j < 16; ++j) o[j] = __float_as_uint(gated_mul<EPI>(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1])));
+            for (int j = 0; j < 16; ++j) {
+                const float bg = y + 2 * j < y_rows ? glu.bias[y + 2 * j] : 0.f, bu = y + 2 * j + 1 < y_rows ? glu.bias[y + 2 * j + 1] : 0.f;
+                o[j] = __float_as_uint(gated_mul<EPI>(__uint_as_float(r[2 * j]) + bg, __uint_as_float(r[2 * j + 1]) + bu, glu));
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) o[j] = __float_as_uint(gated_mul<EPI>(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]), glu));
+        }
         TC* dst = base + (size_t)x * ld + y / 2;
         const int valid = min(16, (y_rows - y) / 2);
         if (valid >= 16 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0 && sizeof(TC) == 2) {
@@ -475,7 +501,7 @@ template <typename TC, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y, TC* __restrict__ out,
                                long long ld, int x_rows, int y_rows, int k_blocks, int x_tiles, int num_tiles, int stream_tiles, int per_block,
-                               float* workspace, int* status)
+                               float* workspace, int* status, GluArgs glu)
 {
     using T = WideTile;
     constexpr int BN = T::BN;
@@ -671,7 +697,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const 
                         r[4 * j + 2] = __float_as_uint(__uint_as_float(r[4 * j + 2]) + v.z);
                         r[4 * j + 3] = __float_as_uint(__uint_as_float(r[4 * j + 3]) + v.w);
                     }
-                    store_chunk_normal<TC, EPI>(out, ld, x, y0 + c, x_rows, y_rows, r);
+                    store_chunk_normal<TC, EPI>(out, ld, x, y0 + c, x_rows, y_rows, r, glu);
                 }
             } else {
 #pragma unroll 1
@@ -679,7 +705,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const 
                     uint32_t r[32];
                     tmem_load<32>(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c), r);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    store_chunk_normal<TC, EPI>(out, ld, x, y0 + c, x_rows, y_rows, r);
+                    store_chunk_normal<TC, EPI>(out, ld, x, y0 + c, x_rows, y_rows, r, glu);
                 }
             }
             if (helpers_kb > 0) {
@@ -802,7 +828,7 @@ template <typename TC, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y, TC* __restrict__ out,
                          long long ld, int x_rows, int y_rows, int k_blocks, int x_tiles, int num_tiles, int splits, int kb_per_split,
-                         long long split_stride, int tail_tiles, int tail_p, int tail_x, float* __restrict__ workspace, int* status)
+                         long long split_stride, int tail_tiles, int tail_p, int tail_x, float* __restrict__ workspace, int* status, GluArgs glu)
 {
     // splits > 1 (few tiles, 512 tokens or so): a work unit is one tile over one range of kb_per_split K blocks; unit u is
     // tile u % num_tiles of range u / num_tiles, and its 32-bit partial tile goes to out + range * split_stride (the
@@ -938,7 +964,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
                     uint32_t r[32];
                     tmem_load<32>(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c), r);
                     tmem_wait_ld();
-                    store_chunk_normal<TC, EPI>(unit_out, ld, x, y0 + c, x_rows, y_rows, r);
+                    store_chunk_normal<TC, EPI>(unit_out, ld, x, y0 + c, x_rows, y_rows, r, glu);
                 }
                 fence_before_sync();
                 if (rank == 0) mbar_arrive(acc_empty + buf);
@@ -1009,7 +1035,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
                     r[4 * j + 2] = __float_as_uint(sum[j].z);
                     r[4 * j + 3] = __float_as_uint(sum[j].w);
                 }
-                store_chunk_normal<TC, EPI>(unit_out, ld, x, y0 + c, x_rows, y_rows, r);
+                store_chunk_normal<TC, EPI>(unit_out, ld, x, y0 + c, x_rows, y_rows, r, glu);
             }
             if (row == 0) g_pair_tail_count[tile_rel * 2 + (int)rank] = 0;   // for the next product: nobody else touches it in this one
         }
@@ -1074,7 +1100,7 @@ static int reduce_splits(const float* scratch, void* C, int c_dtype, long long l
 
 template <int BN, typename TC, int EPI>
 static int launch(const CUtensorMap& mx, const CUtensorMap& my, void* out, long long ld, long long split_stride, int x_rows, int y_rows,
-                  int k_blocks, int splits, int tile_rows, int* status, cudaStream_t stream, const void* next_weights, long long next_bytes)
+                  int k_blocks, int splits, int tile_rows, int* status, cudaStream_t stream, const void* next_weights, long long next_bytes, GluArgs glu)
 {
     using T = Tile<BN>;
     auto kernel = gemm_tcgen05_kernel<BN, TC, EPI>;
@@ -1085,7 +1111,7 @@ static int launch(const CUtensorMap& mx, const CUtensorMap& my, void* out, long 
     dim3 grid((y_rows + BN - 1) / BN, (x_rows + tile_rows - 1) / tile_rows, splits);   // token tiles fastest
     if (grid.y > 65535 || grid.z > 65535) SPY_FAIL("gemm_tcgen05: the grid %u x %u x %u exceeds the launch limits", grid.x, grid.y, grid.z);
     spy_launch(kernel, grid, dim3(NUM_THREADS), T::SMEM, stream, mx, my, (TC*)out, ld, split_stride, x_rows, y_rows, k_blocks, per_split, tile_rows,
-               status, (const uint8_t*)next_weights, next_bytes);
+               status, (const uint8_t*)next_weights, next_bytes, glu);
     SPY_CHECK_LAUNCH("gemm_tcgen05");
     return 0;
 }
@@ -1271,9 +1297,10 @@ extern "C" int spy_gemm_tcgen05_plan(int M, int N, int K, long long scratch_limi
 // next_weights / next_bytes (may be null / 0; used by products of up to 256 tokens only): memory that a
 // later kernel of the stream will read, typically the next product's weights; the blocks ask for it to
 // be brought into L2 once their own loads are requested.  16-byte aligned.
-extern "C" int spy_gemm_tcgen05_ex(const void* A, long long lda, const void* W, long long ldw, void* C, int c_dtype, long long ldc, int M, int N,
-                                   int K, float* scratch, long long scratch_floats, int epilogue, int defer_reduce, int* splits_used,
-                                   int* status, cudaStream_t stream, const void* next_weights, long long next_bytes)
+// epilogue 4: as 1 with the clamped activation and the rows' bias (GluArgs).
+static int run_gemm_tcgen05(const void* A, long long lda, const void* W, long long ldw, void* C, int c_dtype, long long ldc, int M, int N,
+                            int K, float* scratch, long long scratch_floats, int epilogue, int defer_reduce, int* splits_used,
+                            int* status, cudaStream_t stream, const void* next_weights, long long next_bytes, GluArgs glu)
 {
     if (next_weights == nullptr || next_bytes <= 0 || (reinterpret_cast<uintptr_t>(next_weights) & 15)) {
         next_weights = nullptr;
@@ -1285,9 +1312,10 @@ extern "C" int spy_gemm_tcgen05_ex(const void* A, long long lda, const void* W, 
     if (lda % 8 != 0 || ldw % 8 != 0) SPY_FAIL("gemm_tcgen05: row strides %lld/%lld must be multiples of 8 elements", lda, ldw);
     if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(W) & 15)) SPY_FAIL("gemm_tcgen05: operands must be 16-byte aligned");
     if (c_dtype != SPY_F32 && c_dtype != SPY_BF16) SPY_FAIL("gemm_tcgen05: unknown output dtype code %d", c_dtype);
-    if (epilogue < 0 || epilogue > 3) SPY_FAIL("gemm_tcgen05: unknown epilogue %d", epilogue);
+    if (epilogue < 0 || epilogue > 4) SPY_FAIL("gemm_tcgen05: unknown epilogue %d", epilogue);
+    if (epilogue == 4 && !(glu.limit > 0.f)) SPY_FAIL("gemm_tcgen05: the clamped epilogue needs a positive limit");
     if (epilogue == 2 && c_dtype != SPY_BF16) SPY_FAIL("gemm_tcgen05: the relu-squared epilogue needs bfloat16 output");
-    if ((epilogue == 1 || epilogue == 3) && (N % 2 != 0 || c_dtype != SPY_BF16)) SPY_FAIL("gemm_tcgen05: a gated epilogue needs an even N and bfloat16 output");
+    if ((epilogue == 1 || epilogue == 3 || epilogue == 4) && (N % 2 != 0 || c_dtype != SPY_BF16)) SPY_FAIL("gemm_tcgen05: a gated epilogue needs an even N and bfloat16 output");
     Plan plan = make_plan(M, N, K, epilogue == 0);
     if (plan.splits > 1 && (scratch == nullptr || (long long)plan.splits * M * N > scratch_floats)) plan = make_plan(M, N, K, false);
     const int splits = plan.splits;
@@ -1323,6 +1351,7 @@ extern "C" int spy_gemm_tcgen05_ex(const void* A, long long lda, const void* W, 
             SPY_CUDA(cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<bf16, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PAIR_SMEM));
             SPY_CUDA(cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<bf16, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PAIR_SMEM));
             SPY_CUDA(cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<bf16, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PAIR_SMEM));
+            SPY_CUDA(cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<bf16, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PAIR_SMEM));
             const int sms = spy_sm_count();
             cudaLaunchConfig_t cfg = {};
             cfg.gridDim = dim3(sms / 2 * 2);
@@ -1346,7 +1375,7 @@ extern "C" int spy_gemm_tcgen05_ex(const void* A, long long lda, const void* W, 
         if (splits > 1) {
             // ranges of K: 32-bit partial tiles into the scratch, [range][M][N]
             spy_launch_cluster(gemm_tcgen05_pair_kernel<float, 0>, dim3(2 * clusters), dim3(NUM_THREADS), PAIR_SMEM, stream, 2u, mx, my_half, (float*)scratch,
-                               (long long)N, M, N, k_blocks, x_tiles, (int)num_tiles, splits, kb_per_split, split_stride, 0, 1, 0, (float*)nullptr, status);
+                               (long long)N, M, N, k_blocks, x_tiles, (int)num_tiles, splits, kb_per_split, split_stride, 0, 1, 0, (float*)nullptr, status, glu);
             SPY_CHECK_LAUNCH("gemm_tcgen05 (pairs, K ranges)");
             if (!defer_reduce) {
                 if (int rc = reduce_splits(scratch, C, c_dtype, ldc, M, N, splits, stream)) return rc;
@@ -1371,19 +1400,22 @@ extern "C" int spy_gemm_tcgen05_ex(const void* A, long long lda, const void* W, 
         }
         if (epilogue == 2)
             spy_launch_cluster(gemm_tcgen05_pair_kernel<bf16, 2>, dim3(2 * clusters), dim3(NUM_THREADS), PAIR_SMEM, stream, 2u, mx, my_half, (bf16*)C, ldc,
-                               M, N, k_blocks, x_tiles, (int)num_tiles, 1, k_blocks, 0LL, tail_tiles, tail_p, tail_x, scratch, status);
+                               M, N, k_blocks, x_tiles, (int)num_tiles, 1, k_blocks, 0LL, tail_tiles, tail_p, tail_x, scratch, status, glu);
         else if (epilogue == 1)
             spy_launch_cluster(gemm_tcgen05_pair_kernel<bf16, 1>, dim3(2 * clusters), dim3(NUM_THREADS), PAIR_SMEM, stream, 2u, mx, my_half, (bf16*)C, ldc,
-                               M, N, k_blocks, x_tiles, (int)num_tiles, 1, k_blocks, 0LL, tail_tiles, tail_p, tail_x, scratch, status);
+                               M, N, k_blocks, x_tiles, (int)num_tiles, 1, k_blocks, 0LL, tail_tiles, tail_p, tail_x, scratch, status, glu);
         else if (epilogue == 3)
             spy_launch_cluster(gemm_tcgen05_pair_kernel<bf16, 3>, dim3(2 * clusters), dim3(NUM_THREADS), PAIR_SMEM, stream, 2u, mx, my_half, (bf16*)C, ldc,
-                               M, N, k_blocks, x_tiles, (int)num_tiles, 1, k_blocks, 0LL, tail_tiles, tail_p, tail_x, scratch, status);
+                               M, N, k_blocks, x_tiles, (int)num_tiles, 1, k_blocks, 0LL, tail_tiles, tail_p, tail_x, scratch, status, glu);
+        else if (epilogue == 4)
+            spy_launch_cluster(gemm_tcgen05_pair_kernel<bf16, 4>, dim3(2 * clusters), dim3(NUM_THREADS), PAIR_SMEM, stream, 2u, mx, my_half, (bf16*)C, ldc,
+                               M, N, k_blocks, x_tiles, (int)num_tiles, 1, k_blocks, 0LL, tail_tiles, tail_p, tail_x, scratch, status, glu);
         else if (c_dtype == SPY_F32)
             spy_launch_cluster(gemm_tcgen05_pair_kernel<float, 0>, dim3(2 * clusters), dim3(NUM_THREADS), PAIR_SMEM, stream, 2u, mx, my_half, (float*)C, ldc,
-                               M, N, k_blocks, x_tiles, (int)num_tiles, 1, k_blocks, 0LL, tail_tiles, tail_p, tail_x, scratch, status);
+                               M, N, k_blocks, x_tiles, (int)num_tiles, 1, k_blocks, 0LL, tail_tiles, tail_p, tail_x, scratch, status, glu);
         else
             spy_launch_cluster(gemm_tcgen05_pair_kernel<bf16, 0>, dim3(2 * clusters), dim3(NUM_THREADS), PAIR_SMEM, stream, 2u, mx, my_half, (bf16*)C, ldc,
-                               M, N, k_blocks, x_tiles, (int)num_tiles, 1, k_blocks, 0LL, tail_tiles, tail_p, tail_x, scratch, status);
+                               M, N, k_blocks, x_tiles, (int)num_tiles, 1, k_blocks, 0LL, tail_tiles, tail_p, tail_x, scratch, status, glu);
         SPY_CHECK_LAUNCH("gemm_tcgen05 (pairs)");
         return 0;
     }
@@ -1421,33 +1453,38 @@ extern "C" int spy_gemm_tcgen05_ex(const void* A, long long lda, const void* W, 
             SPY_CUDA(cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<bf16, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WideTile::SMEM));
             SPY_CUDA(cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<bf16, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WideTile::SMEM));
             SPY_CUDA(cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<bf16, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WideTile::SMEM));
+            SPY_CUDA(cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<bf16, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WideTile::SMEM));
         }
         if (epilogue == 2)
             spy_launch(gemm_tcgen05_persistent_kernel<bf16, 2>, dim3(grid), dim3(NUM_THREADS), WideTile::SMEM, stream, mx, my, (bf16*)C, ldc, M, N,
-                       k_blocks, x_tiles, (int)num_tiles, stream_tiles, per_block, scratch, status);
+                       k_blocks, x_tiles, (int)num_tiles, stream_tiles, per_block, scratch, status, glu);
         else if (epilogue == 1)
             spy_launch(gemm_tcgen05_persistent_kernel<bf16, 1>, dim3(grid), dim3(NUM_THREADS), WideTile::SMEM, stream, mx, my, (bf16*)C, ldc, M, N,
-                       k_blocks, x_tiles, (int)num_tiles, stream_tiles, per_block, scratch, status);
+                       k_blocks, x_tiles, (int)num_tiles, stream_tiles, per_block, scratch, status, glu);
         else if (epilogue == 3)
             spy_launch(gemm_tcgen05_persistent_kernel<bf16, 3>, dim3(grid), dim3(NUM_THREADS), WideTile::SMEM, stream, mx, my, (bf16*)C, ldc, M, N,
-                       k_blocks, x_tiles, (int)num_tiles, stream_tiles, per_block, scratch, status);
+                       k_blocks, x_tiles, (int)num_tiles, stream_tiles, per_block, scratch, status, glu);
+        else if (epilogue == 4)
+            spy_launch(gemm_tcgen05_persistent_kernel<bf16, 4>, dim3(grid), dim3(NUM_THREADS), WideTile::SMEM, stream, mx, my, (bf16*)C, ldc, M, N,
+                       k_blocks, x_tiles, (int)num_tiles, stream_tiles, per_block, scratch, status, glu);
         else if (c_dtype == SPY_F32)
             spy_launch(gemm_tcgen05_persistent_kernel<float, 0>, dim3(grid), dim3(NUM_THREADS), WideTile::SMEM, stream, mx, my, (float*)C, ldc, M, N,
-                       k_blocks, x_tiles, (int)num_tiles, stream_tiles, per_block, scratch, status);
+                       k_blocks, x_tiles, (int)num_tiles, stream_tiles, per_block, scratch, status, glu);
         else
             spy_launch(gemm_tcgen05_persistent_kernel<bf16, 0>, dim3(grid), dim3(NUM_THREADS), WideTile::SMEM, stream, mx, my, (bf16*)C, ldc, M, N,
-                       k_blocks, x_tiles, (int)num_tiles, stream_tiles, per_block, scratch, status);
+                       k_blocks, x_tiles, (int)num_tiles, stream_tiles, per_block, scratch, status, glu);
         SPY_CHECK_LAUNCH("gemm_tcgen05 (persistent)");
         return 0;
     }
     if (!swap) SPY_FAIL("gemm_tcgen05: no kernel was chosen for M=%d N=%d K=%d (splits %d)", M, N, K, splits);
     int rc;
 #define SPY_LAUNCH(BN_)                                                                                                             \
-    rc = epilogue == 2 ? launch<BN_, bf16, 2>(mx, my, out, ld, split_stride, x_rows, y_rows, k_blocks, splits, plan.tile_rows, status, stream, next_weights, next_bytes)   \
-         : epilogue == 1 ? launch<BN_, bf16, 1>(mx, my, out, ld, split_stride, x_rows, y_rows, k_blocks, splits, plan.tile_rows, status, stream, next_weights, next_bytes)   \
-         : epilogue == 3 ? launch<BN_, bf16, 3>(mx, my, out, ld, split_stride, x_rows, y_rows, k_blocks, splits, plan.tile_rows, status, stream, next_weights, next_bytes)   \
-         : f32_out     ? launch<BN_, float, 0>(mx, my, out, ld, split_stride, x_rows, y_rows, k_blocks, splits, plan.tile_rows, status, stream, next_weights, next_bytes)  \
-                       : launch<BN_, bf16, 0>(mx, my, out, ld, split_stride, x_rows, y_rows, k_blocks, splits, plan.tile_rows, status, stream, next_weights, next_bytes)
+    rc = epilogue == 2 ? launch<BN_, bf16, 2>(mx, my, out, ld, split_stride, x_rows, y_rows, k_blocks, splits, plan.tile_rows, status, stream, next_weights, next_bytes, glu)   \
+         : epilogue == 1 ? launch<BN_, bf16, 1>(mx, my, out, ld, split_stride, x_rows, y_rows, k_blocks, splits, plan.tile_rows, status, stream, next_weights, next_bytes, glu)   \
+         : epilogue == 3 ? launch<BN_, bf16, 3>(mx, my, out, ld, split_stride, x_rows, y_rows, k_blocks, splits, plan.tile_rows, status, stream, next_weights, next_bytes, glu)   \
+         : epilogue == 4 ? launch<BN_, bf16, 4>(mx, my, out, ld, split_stride, x_rows, y_rows, k_blocks, splits, plan.tile_rows, status, stream, next_weights, next_bytes, glu)   \
+         : f32_out     ? launch<BN_, float, 0>(mx, my, out, ld, split_stride, x_rows, y_rows, k_blocks, splits, plan.tile_rows, status, stream, next_weights, next_bytes, glu)  \
+                       : launch<BN_, bf16, 0>(mx, my, out, ld, split_stride, x_rows, y_rows, k_blocks, splits, plan.tile_rows, status, stream, next_weights, next_bytes, glu)
     if (bn == 16) SPY_LAUNCH(16);
     else if (bn == 32) SPY_LAUNCH(32);
     else if (bn == 128) SPY_LAUNCH(128);
@@ -1458,6 +1495,28 @@ extern "C" int spy_gemm_tcgen05_ex(const void* A, long long lda, const void* W, 
     return 0;
 }
 
+
+extern "C" int spy_gemm_tcgen05_ex(const void* A, long long lda, const void* W, long long ldw, void* C, int c_dtype, long long ldc, int M, int N,
+                                   int K, float* scratch, long long scratch_floats, int epilogue, int defer_reduce, int* splits_used,
+                                   int* status, cudaStream_t stream, const void* next_weights, long long next_bytes)
+{
+    if (epilogue == 4) SPY_FAIL("gemm_tcgen05: the clamped epilogue has an entry of its own");
+    const GluArgs none = {nullptr, 0.f, 0.f};
+    return run_gemm_tcgen05(A, lda, W, ldw, C, c_dtype, ldc, M, N, K, scratch, scratch_floats, epilogue, defer_reduce, splits_used, status, stream,
+                            next_weights, next_bytes, none);
+}
+
+// The gated product with the clamped activation in its epilogue: W's rows alternate gate and up rows, bias (null, or [N] float32 in the
+// rows' order) is added to the product, then C[m, i] = g * sigmoid(slope g) * (u + 1) with g = min(gate, limit), u = clamp(up, -limit,
+// limit); C is [M, N / 2] bfloat16, K is not split.
+extern "C" int spy_gemm_tcgen05_clamped(const void* A, long long lda, const void* W, long long ldw, void* C, long long ldc, int M, int N, int K,
+                                        float* scratch, long long scratch_floats, const float* bias, float limit, float slope, int* status,
+                                        cudaStream_t stream, const void* next_weights, long long next_bytes)
+{
+    const GluArgs glu = {bias, limit, slope};
+    return run_gemm_tcgen05(A, lda, W, ldw, C, SPY_BF16, ldc, M, N, K, scratch, scratch_floats, 4, 0, nullptr, status, stream, next_weights, next_bytes,
+                            glu);
+}
 
 // The plain product: no epilogue, partial products summed before it returns.
 extern "C" int spy_gemm_tcgen05(const void* A, long long lda, const void* W, long long ldw, void* C, int c_dtype, long long ldc, int M, int N,

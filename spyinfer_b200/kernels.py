@@ -953,7 +953,7 @@ def _scratch(device) -> torch.Tensor:
 
 def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None,
                  out_dtype: Optional[torch.dtype] = None, epilogue: Optional[str] = None, defer: bool = False,
-                 prefetch: Optional[torch.Tensor] = None, prefetch_bytes: int = 0) -> torch.Tensor:
+                 prefetch: Optional[torch.Tensor] = None, prefetch_bytes: int = 0, glu: Optional[tuple] = None) -> torch.Tensor:
     """``a[M, K] @ w[N, K]^T`` on the tensor cores: bfloat16 operands, 32-bit accumulation,
     bfloat16 or float32 output.  K must be a multiple of 8.
 
@@ -972,11 +972,19 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] =
         raise KernelError(f"gemm: the weight's rows must start on 16-byte borders (row distance {ldw}, address {w.data_ptr():#x})")
     if w.shape[1] != K:
         raise KernelError(f"gemm: shapes do not fit: input {tuple(a.shape)}, weight {tuple(w.shape)}")
-    if epilogue not in (None, "swiglu", "relu2", "geglu_tanh"):
+    if epilogue not in (None, "swiglu", "relu2", "geglu_tanh", "clamped_swish"):
         raise KernelError(f"gemm: unknown epilogue {epilogue!r}")
+    if epilogue == "clamped_swish":
+        # glu = (bias or None, limit, slope): the bias [N] float32 lies in the order of the weight's rows (gate and up in turns)
+        if glu is None or (out_dtype or torch.bfloat16) != torch.bfloat16:
+            raise KernelError("gemm: the clamped epilogue needs its (bias, limit, slope) and writes bfloat16")
+        if glu[0] is not None:
+            _check(glu[0], "gate|up bias", torch.float32, 1)
+            if glu[0].shape[0] != N:
+                raise KernelError("gemm: the clamped epilogue's bias has one entry per weight row")
     if epilogue == "relu2" and (out_dtype or torch.bfloat16) != torch.bfloat16:
         raise KernelError("gemm: the relu2 epilogue writes bfloat16")
-    n_out = N // 2 if epilogue in ("swiglu", "geglu_tanh") else N
+    n_out = N // 2 if epilogue in ("swiglu", "geglu_tanh", "clamped_swish") else N
     if status is None:
         status = status_word(a.device)
     lib = build.load("gemm_tcgen05")
@@ -1003,6 +1011,11 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] =
         if tuple(out.shape) != (M, n_out):
             raise KernelError(f"gemm: output {tuple(out.shape)} does not fit [{M}, {n_out}]")
     scratch = _scratch(a.device)
+    if epilogue == "clamped_swish":
+        _call("gemm_tcgen05", "spy_gemm_tcgen05_clamped", _ptr(a), ctypes.c_longlong(K), _ptr(w), ctypes.c_longlong(ldw), _ptr(out), ctypes.c_longlong(n_out),
+              M, N, K, _ptr(scratch), ctypes.c_longlong(scratch.numel()), _ptr(glu[0]), ctypes.c_float(glu[1]), ctypes.c_float(glu[2]), _ptr(status),
+              _stream(), pf_ptr, ctypes.c_longlong(pf_bytes))
+        return out
     _call("gemm_tcgen05", "spy_gemm_tcgen05_ex", _ptr(a), ctypes.c_longlong(K), _ptr(w), ctypes.c_longlong(ldw), _ptr(out),
           _code(out, "gemm output"), ctypes.c_longlong(n_out), M, N, K, _ptr(scratch), ctypes.c_longlong(scratch.numel()),
           {None: 0, "swiglu": 1, "relu2": 2, "geglu_tanh": 3}[epilogue], 0, None, _ptr(status), _stream(), pf_ptr, ctypes.c_longlong(pf_bytes))

@@ -103,16 +103,19 @@ class GatedMLP(FeedForward):
         gate, up = tensors[p + n["gate"]], tensors[p + n["up"]]
         if gate.dtype != up.dtype:
             gate, up = gate.float(), up.float()
-        self.fused = (self.ctx.dtype == torch.bfloat16 and gate.dtype == torch.bfloat16 and self.activation in ("silu", "gelu_tanh") and not self.has_bias
-                      and kernels.tensor_core_gemm_takes(2 * self.inter, self.hidden))
+        # silu and gelu_tanh without biases, and the clamped activation with or without them, run in the tensor-core product's epilogue
+        self.fused = (self.ctx.dtype == torch.bfloat16 and gate.dtype == torch.bfloat16 and kernels.tensor_core_gemm_takes(2 * self.inter, self.hidden)
+                      and (self.activation == "clamped_swish" or (self.activation in ("silu", "gelu_tanh") and not self.has_bias)))
         if self.fused:
             # rows alternate gate_i, up_i: the tensor-core product applies act(gate) * up in its epilogue
             self.gate_up = Linear(torch.stack([gate, up], dim=1).reshape(2 * self.inter, self.hidden).contiguous(), self.ctx.dtype)
         else:
             self.gate_up = Linear(torch.cat([gate, up], dim=0).contiguous(), self.ctx.dtype)
         if self.has_bias:
-            # the gate and up biases are added by the activation's kernel (32-bit), the down bias by a pass behind its product
-            self.gate_up_bias = torch.cat([tensors[p + n["gate"] + ".b"].float(), tensors[p + n["up"] + ".b"].float()]).contiguous()
+            # the gate and up biases are added where the activation is computed (32-bit; in the rows' order: alternating when the
+            # product's epilogue does it), the down bias by a pass behind its product or by the consumer
+            gb, ub = tensors[p + n["gate"] + ".b"].float(), tensors[p + n["up"] + ".b"].float()
+            self.gate_up_bias = (torch.stack([gb, ub], dim=1).reshape(-1) if self.fused else torch.cat([gb, ub])).contiguous()
         down_bias = tensors[p + n["down"] + ".b"].float().contiguous() if self.has_bias else None
         if self.leave_output_bias:           # the consumer adds it (and may then take the down product's split-K parts unsummed)
             self.output_bias, down_bias = down_bias, None
@@ -126,6 +129,8 @@ class GatedMLP(FeedForward):
         return ([] if self.fused else ["swiglu"]) + self.gate_up.modules() + self.down.modules()
 
     def forward(self, x):
+        if self.fused and self.activation == "clamped_swish":
+            return self.down(self.gate_up(x, epilogue="clamped_swish", glu=(self.gate_up_bias, self.limit, self.slope)), defer=self.defer_output)
         if self.fused:
             return self.down(self.gate_up(x, epilogue="swiglu" if self.activation == "silu" else "geglu_tanh"), defer=self.defer_output)
         z = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)

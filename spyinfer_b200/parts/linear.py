@@ -49,23 +49,25 @@ class Linear:
     def modules(self) -> List[str]:
         return (["gemm_tcgen05"] if self.fast else ["gemm_simt"]) + (["swiglu"] if self.bias is not None else [])
 
-    def __call__(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None, epilogue: Optional[str] = None, defer: bool = False) -> torch.Tensor:
+    def __call__(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None, epilogue: Optional[str] = None, defer: bool = False,
+                 glu: Optional[tuple] = None) -> torch.Tensor:
         """``epilogue="swiglu"`` (tensor-core kernel only; the weight's rows must alternate gate
         and up rows) returns ``silu(gate) * up``; ``epilogue="relu2"`` (tensor-core kernel only) the square of relu of the
-        product.  ``defer=True`` allows the result to come back
+        product; ``epilogue="clamped_swish"`` with ``glu = (bias of the alternating rows or None, limit, slope)`` the clamped gated
+        activation.  ``defer=True`` allows the result to come back
         as a stack ``[splits, rows, out]`` of float32 partial products that the consumer sums."""
         if self.bias is not None:
             if epilogue is not None:
                 raise ValueError("a product with a bias takes no fused epilogue")
             defer = False
-        y = self._product(x, out_dtype, epilogue, defer)
+        y = self._product(x, out_dtype, epilogue, defer, glu)
         return kernels.add_bias(y, self.bias) if self.bias is not None else y
 
-    def _product(self, x, out_dtype, epilogue, defer):
+    def _product(self, x, out_dtype, epilogue, defer, glu=None):
         if self.fast:
             hint = self.next_weight if self.hint_next and x.shape[0] <= 256 and self.prefetch_bytes > 0 else None
             return kernels.gemm_tcgen05(x, self.weight, out_dtype=out_dtype or x.dtype, epilogue=epilogue, defer=defer,
-                                        prefetch=hint, prefetch_bytes=self.prefetch_bytes)
+                                        prefetch=hint, prefetch_bytes=self.prefetch_bytes, glu=glu)
         if epilogue is not None:
             raise ValueError("only the tensor-core product has fused epilogues")
         out = torch.empty((x.shape[0], self.out_features), dtype=out_dtype or x.dtype, device=x.device)

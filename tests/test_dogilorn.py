@@ -488,6 +488,27 @@ def test_clamped_gate_with_the_biases_folded_in(dtype):
 
 
 @gpu
+@pytest.mark.parametrize("M", [1, 8, 40, 100, 128, 200, 300, 640, 1200, 2048])
+@pytest.mark.parametrize("N,K,bias", [(320, 136, True), (4096, 1024, True), (6400, 2048, False), (3364, 512, True)])
+def test_product_with_the_clamped_gate_and_the_biases_in_its_epilogue(M, N, K, bias):
+    """The tensor-core product over alternating gate and up rows adds the rows' biases and hands out the clamped gated
+    activation, on every kernel that the number of tokens selects (and with a last tile of rows that is not full)."""
+    from spyinfer_b200 import kernels
+
+    g = torch.Generator().manual_seed(M + N)
+    a = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (2.0 * torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    b = (0.5 * torch.randn(N, generator=g)) if bias else None
+    limit = 1.3
+    out = kernels.gemm_tcgen05(a.cuda(), w.cuda(), epilogue="clamped_swish", glu=(b.cuda() if bias else None, limit, 1.702))
+    prod = a.double() @ w.double().T + (b.double() if bias else 0.0)
+    gate, up = torch.clamp(prod[:, 0::2], max=limit), torch.clamp(prod[:, 1::2], -limit, limit)
+    want = gate * torch.sigmoid(1.702 * gate) * (up + 1.0)
+    assert out.dtype == torch.bfloat16 and tuple(out.shape) == (M, N // 2)
+    assert torch.allclose(out.float().cpu().double(), want, atol=2e-2, rtol=2e-2)
+
+
+@gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("experts,identity,top,ff,groups,shared", [(6, 2, 3, 24, (4, 2), 40), (5, 0, 1, 16, None, 0), (13, 3, 4, 32, (4, 2), 64), (4, 0, 4, 12, None, 8),
                                                                    (3, 1, 2, 8, (2, 1), 16), (2, 2, 2, 16, (2, 2), 0), (60, 4, 6, 8, (8, 3), 0)])
