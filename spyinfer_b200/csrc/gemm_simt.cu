@@ -68,10 +68,10 @@ gemm_simt_kernel(const TA* __restrict__ A, long long lda, const TW* __restrict__
 
 // Row strides lda/ldw/ldc are in elements.
 
-// A product with few output columns (a router, a gate of one number a token): a block of four warps owns one row of A and
+// A product with few output columns (a router, a gate of one number a token): a block of eight warps owns one row of A (or four) and
 // up to SKINNY_NG columns at a time; its threads stride over k, so every load is a run of consecutive elements and many are
 // under way at once, and the threads' sums are added in a fixed order.  A row's result does not depend on M either.
-constexpr int SKINNY_N = 32, SKINNY_NG = 16, SKINNY_THREADS = 128;
+constexpr int SKINNY_N = 32, SKINNY_NG = 16, SKINNY_THREADS = 256;
 
 // ROWS rows of A a block: with many rows every weight element a block fetches serves ROWS of them (each block reads all of W, so
 // with one row a block the weights cross the L2 once a row).  A row's sums are formed in the same order whatever ROWS is.
@@ -93,7 +93,7 @@ gemm_skinny_kernel(const TA* __restrict__ A, long long lda, const TW* __restrict
         for (int r = 0; r < ROWS; ++r)
 #pragma unroll
             for (int j = 0; j < SKINNY_NG; ++j) acc[r][j] = 0.f;
-#pragma unroll 2
+#pragma unroll 4
         for (int k = threadIdx.x; k < K; k += SKINNY_THREADS) {
             float av[ROWS];
 #pragma unroll

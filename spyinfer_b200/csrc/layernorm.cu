@@ -4,7 +4,9 @@
 //   out    = (v - mean(v)) / sqrt(mean((v - mean(v))^2) + eps) * w (+ bias)          32-bit statistics, two passes
 // a_w (null, or [len] of the weight's type) multiplies the first result element by element along the row (a layer scale);
 // a_bias (null, or [len] float32) is added to the first result ahead of that: x += scale_a * a_w * (sum_s a[s] + a_bias), the
-// bias of the projection that made the result.
+// bias of the projection that made the result.  a_rows (null, or [*, len] of the output's type) with a_row_w ([*] float32): a second
+// term of the first result with one weight a row, x += scale_a * a_w * (sum_s a[s] + a_bias + a_row_w[row] * a_rows[row]), what the
+// identity experts of a mixture contribute (their summed weight times the feed-forward's input).
 // a and b are null, one array [*, len], or stacks of split-K partial products (splits arrays, split_stride elements
 // apart); two of them because a layer whose mixer is two mixers side by side hands over two results with a weight each.
 // With center == 0 the mean is not removed (an RMS norm with the same fused sums).
@@ -43,7 +45,8 @@ template <typename TX, typename TD, typename TW, typename TO, bool VEC>
 __global__ void __launch_bounds__(1024)
 layernorm_kernel(TX* x, const TD* __restrict__ a, int a_splits, long long a_stride, float a_scale, const TD* __restrict__ b, int b_splits,
                  long long b_stride, float b_scale, const int* __restrict__ rows, const TW* __restrict__ w, TO* __restrict__ out, int len, float eps,
-                 int write_back, int center, const TW* __restrict__ bias, const TW* __restrict__ a_w, const float* __restrict__ a_bias)
+                 int write_back, int center, const TW* __restrict__ bias, const TW* __restrict__ a_w, const float* __restrict__ a_bias,
+                 const TO* __restrict__ a_rows, const float* __restrict__ a_row_w)
 {
     extern __shared__ __align__(16) float row_buf[];  // len floats, then 33 of scratch
     pdl_enter();
@@ -65,6 +68,13 @@ layernorm_kernel(TX* x, const TD* __restrict__ a, int a_splits, long long a_stri
                 if constexpr (VEC) Quad<TD>::load(ar + (size_t)s * a_stride + i, p); else p[0] = to_f32(ar[(size_t)s * a_stride + i]);
 #pragma unroll
                 for (int e = 0; e < E; ++e) d[e] += p[e];
+            }
+            if (a_rows) {
+                const float rw = a_row_w[src_row];
+                float xr4[4];
+                if constexpr (VEC) Quad<TO>::load(a_rows + (size_t)src_row * len + i, xr4); else xr4[0] = to_f32(a_rows[(size_t)src_row * len + i]);
+#pragma unroll
+                for (int e = 0; e < E; ++e) d[e] = fmaf(rw, xr4[e], d[e]);
             }
             if (a_bias) {
                 float ab[4];
@@ -131,7 +141,8 @@ layernorm_kernel(TX* x, const TD* __restrict__ a, int a_splits, long long a_stri
 // out: [n, len] of out_dtype.  write_back stores the sum into x and needs rows == null.  bias, a_w: null or [len] of w_dtype.
 static int run_layernorm(void* x, int x_dtype, const void* a, int a_splits, long long a_stride, float a_scale, const void* b, int b_splits,
                          long long b_stride, float b_scale, int delta_dtype, const int* rows, const void* w, int w_dtype, void* out, int out_dtype,
-                         int n, int len, float eps, int write_back, int center, const void* bias, const void* a_w, const float* a_bias, cudaStream_t stream)
+                         int n, int len, float eps, int write_back, int center, const void* bias, const void* a_w, const float* a_bias, const void* a_rows,
+                         const float* a_row_w, cudaStream_t stream)
 {
     if (n <= 0) return 0;
     if (len <= 0) SPY_FAIL("layernorm: row length %d must be positive", len);
@@ -143,7 +154,7 @@ static int run_layernorm(void* x, int x_dtype, const void* a, int a_splits, long
     if (smem > 227 * 1024) SPY_FAIL("layernorm: a row of %d elements does not fit in shared memory (limit %d)", len, (227 * 1024) / 4 - 33);
     const bool vec = len % 4 == 0 && a_stride % 4 == 0 && b_stride % 4 == 0 &&
                      ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(w) |
-                       reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(bias) | reinterpret_cast<uintptr_t>(a_w) | reinterpret_cast<uintptr_t>(a_bias)) & 15) == 0;
+                       reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(bias) | reinterpret_cast<uintptr_t>(a_w) | reinterpret_cast<uintptr_t>(a_bias) | reinterpret_cast<uintptr_t>(a_rows)) & 15) == 0;
     // many rows: fewer threads a row (two quads each) and so more rows an SM at a time; few rows: the row spread as wide as it goes
     int threads = (len / (vec ? (n >= 512 ? 8 : 4) : 4) + 31) / 32 * 32;
     threads = threads < 64 ? 64 : (threads > 1024 ? 1024 : threads);
@@ -154,7 +165,7 @@ static int run_layernorm(void* x, int x_dtype, const void* a, int a_splits, long
                     auto kernel = vec ? layernorm_kernel<TX, TD, TW, TO, true> : layernorm_kernel<TX, TD, TW, TO, false>;
                     if (smem > 48 * 1024) SPY_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
                     spy_launch(kernel, dim3(n), dim3(threads), smem, stream, (TX*)x, (const TD*)a, a_splits, a_stride, a_scale, (const TD*)b, b_splits,
-                               b_stride, b_scale, rows, (const TW*)w, (TO*)out, len, eps, write_back, center, (const TW*)bias, (const TW*)a_w, a_bias);
+                               b_stride, b_scale, rows, (const TW*)w, (TO*)out, len, eps, write_back, center, (const TW*)bias, (const TW*)a_w, a_bias, (const TO*)a_rows, a_row_w);
                 })
             })
         })
@@ -168,18 +179,20 @@ extern "C" int spy_layernorm(void* x, int x_dtype, const void* a, int a_splits, 
                              int n, int len, float eps, int write_back, int center, cudaStream_t stream)
 {
     return run_layernorm(x, x_dtype, a, a_splits, a_stride, a_scale, b, b_splits, b_stride, b_scale, delta_dtype, rows, w, w_dtype, out, out_dtype, n, len,
-                         eps, write_back, center, nullptr, nullptr, nullptr, stream);
+                         eps, write_back, center, nullptr, nullptr, nullptr, nullptr, nullptr, stream);
 }
 
 // The same with a bias behind the weight and a per-channel multiplier of the first result (each null or [len] of w_dtype), and a
 // bias of the first result itself (null or [len] float32).
-extern "C" int spy_layernorm_affine(void* x, int x_dtype, const void* a, int a_splits, long long a_stride, float a_scale, const void* a_w, const float* a_bias, const void* b,
+extern "C" int spy_layernorm_affine(void* x, int x_dtype, const void* a, int a_splits, long long a_stride, float a_scale, const void* a_w, const float* a_bias,
+                                    const void* a_rows, const float* a_row_w, const void* b,
                                     int b_splits, long long b_stride, float b_scale, int delta_dtype, const int* rows, const void* w, const void* bias,
                                     int w_dtype, void* out, int out_dtype, int n, int len, float eps, int write_back, int center, cudaStream_t stream)
 {
-    if ((a_w != nullptr || a_bias != nullptr) && a == nullptr) SPY_FAIL("layernorm: a per-channel multiplier or a bias without a result to go with");
+    if ((a_w != nullptr || a_bias != nullptr || a_rows != nullptr) && a == nullptr) SPY_FAIL("layernorm: a per-channel multiplier, a bias or a row term without a result to go with");
+    if ((a_rows != nullptr) != (a_row_w != nullptr)) SPY_FAIL("layernorm: a row term comes with its weights");
     return run_layernorm(x, x_dtype, a, a_splits, a_stride, a_scale, b, b_splits, b_stride, b_scale, delta_dtype, rows, w, w_dtype, out, out_dtype, n, len,
-                         eps, write_back, center, bias, a_w, a_bias, stream);
+                         eps, write_back, center, bias, a_w, a_bias, a_rows, a_row_w, stream);
 }
 
 // out = scale_a * sum_s a[s] + scale_b * sum_s b[s], element by element in 32-bit: the weighted sum of two results (each

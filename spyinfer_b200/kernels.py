@@ -179,12 +179,13 @@ def _stack_of(delta: Optional[torch.Tensor], like: torch.Tensor, what: str):
 def layernorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, delta: Optional[torch.Tensor] = None, delta_scale: float = 1.0,
               delta2: Optional[torch.Tensor] = None, delta2_scale: float = 1.0, rows: Optional[torch.Tensor] = None, write_back: bool = False,
               center: bool = True, bias: Optional[torch.Tensor] = None, delta_weight: Optional[torch.Tensor] = None,
-              delta_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+              delta_bias: Optional[torch.Tensor] = None, delta_rows: Optional[tuple] = None) -> torch.Tensor:
     """``out = layer_norm(x + delta_scale * delta_weight * (delta + delta_bias) + delta2_scale * delta2) * weight (+ bias)`` row by row (mean
     removed; ``center=False``: the mean stays, an RMS norm); with ``write_back`` the sum is stored into ``x``; ``rows`` gathers
     rows.  Each delta has x's shape or is a stack ``[splits, rows, len]`` of partial sums that are added in order; both have
     one dtype.  ``bias`` and ``delta_weight`` (a multiplier along the row for ``delta``) are ``[len]`` of the weight's dtype,
-    ``delta_bias`` (the bias of the projection that made ``delta``) ``[len]`` float32."""
+    ``delta_bias`` (the bias of the projection that made ``delta``) ``[len]`` float32.  ``delta_rows = (rows [*, len] of the output's
+    dtype, weights [*] float32)`` adds ``weights[t] * rows[t]`` to ``delta`` (ahead of ``delta_weight``)."""
     _check(x, "layernorm input", ndim=2)
     _check(weight, "layernorm weight", ndim=1)
     _check(out, "layernorm output", ndim=2)
@@ -202,8 +203,13 @@ def layernorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tens
         _check(delta_bias, "layernorm delta bias", torch.float32, 1)
         if delta_bias.shape[0] != H:
             raise KernelError(f"layernorm delta bias: {delta_bias.shape[0]} elements for rows of {H}")
-    if (delta_weight is not None or delta_bias is not None) and delta is None:
-        raise KernelError("layernorm: a delta weight or bias without a delta")
+    if delta_rows is not None:
+        _check(delta_rows[0], "layernorm delta rows", out.dtype, 2)
+        _check(delta_rows[1], "layernorm delta row weights", torch.float32, 1)
+        if tuple(delta_rows[0].shape) != tuple(x.shape) or delta_rows[1].shape[0] != x.shape[0]:
+            raise KernelError("layernorm: the delta's row term has the input's shape and one weight a row")
+    if (delta_weight is not None or delta_bias is not None or delta_rows is not None) and delta is None:
+        raise KernelError("layernorm: a delta weight, bias or row term without a delta")
     a, a_splits, a_stride = _stack_of(delta, x, "layernorm delta")
     b, b_splits, b_stride = _stack_of(delta2, x, "layernorm second delta")
     if a is not None and b is not None and a.dtype != b.dtype:
@@ -215,9 +221,10 @@ def layernorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tens
         n = x.shape[0]
     if out.shape[0] != n:
         raise KernelError(f"layernorm: output has {out.shape[0]} rows, expected {n}")
-    if bias is not None or delta_weight is not None or delta_bias is not None:
+    if bias is not None or delta_weight is not None or delta_bias is not None or delta_rows is not None:
         _call("layernorm", "spy_layernorm_affine", _ptr(x), _code(x, "layernorm input"), _ptr(a), a_splits, ctypes.c_longlong(a_stride),
-              ctypes.c_float(delta_scale), _ptr(delta_weight), _ptr(delta_bias), _ptr(b), b_splits, ctypes.c_longlong(b_stride), ctypes.c_float(delta2_scale),
+              ctypes.c_float(delta_scale), _ptr(delta_weight), _ptr(delta_bias), _ptr(delta_rows[0] if delta_rows is not None else None),
+              _ptr(delta_rows[1] if delta_rows is not None else None), _ptr(b), b_splits, ctypes.c_longlong(b_stride), ctypes.c_float(delta2_scale),
               _code(a, "layernorm delta") if a is not None else 0, _ptr(rows), _ptr(weight), _ptr(bias), _code(weight, "layernorm weight"), _ptr(out),
               _code(out, "layernorm output"), n, H, ctypes.c_float(eps), int(bool(write_back)), int(bool(center)), _stream())
         return out

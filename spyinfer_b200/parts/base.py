@@ -48,11 +48,14 @@ class ChannelScaled:
     """A sublayer output that the stream takes multiplied element by element along the row: ``residual += y * weight``
     with ``weight [size]`` (a layer scale).  ``y`` is ``[rows, size]`` or a stack ``[splits, rows, size]`` of float32 partial
     products.  ``bias`` (optional, float32 ``[size]``): the bias of the projection that made ``y``, still to be added:
-    ``residual += (y + bias) * weight``.  A norm that says ``takes_channel_scale`` forms the product in its own kernel."""
+    ``residual += (y + bias) * weight``.  ``rows`` (optional, ``(x [rows, size] of the activations' type, w [rows] float32)``): one
+    more term with a weight a row, ``residual += (y + bias + w[t] * x[t]) * weight``.  A norm that says ``takes_channel_scale`` forms
+    the product in its own kernel."""
 
     y: torch.Tensor
     weight: torch.Tensor
     bias: Optional[torch.Tensor] = None
+    rows: Optional[Tuple[torch.Tensor, torch.Tensor]] = None
 
 
 @dataclass
@@ -152,6 +155,9 @@ class FeedForward(Part):
     #: bias then leaves it out and offers it as ``output_bias`` (float32 ``[size]``, None when there is none)
     leave_output_bias: bool = False
     output_bias: Optional[torch.Tensor] = None
+    #: set with ``leave_output_bias``: a feed-forward whose result has a term ``w[t] * x[t]`` (a weight a row times its input) may
+    #: leave that to the consumer as well and offers it, after every ``forward``, as ``output_rows = (x, w)`` (else None)
+    output_rows: Optional[Tuple[torch.Tensor, torch.Tensor]] = None
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError

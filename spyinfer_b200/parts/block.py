@@ -145,7 +145,7 @@ class ScaledPreNormBlock(Block):
             return hidden, a
         x = self.ffn_norm.forward_add(hidden, a, scale=self.residual_scale)
         f = self.feed_forward.forward(x)
-        return hidden, self.ffn_scale.defer(f, self.feed_forward.output_bias) if self.ffn_scale is not None else f
+        return hidden, self.ffn_scale.defer(f, self.feed_forward.output_bias, self.feed_forward.output_rows) if self.ffn_scale is not None else f
 
 
 @register_block("sandwich_norm")

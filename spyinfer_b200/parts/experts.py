@@ -118,7 +118,11 @@ class ExpertMixture(FeedForward):
                                identity=self.identity, correction=self.correction, groups=self.groups, activation=self.activation, id_weight=idw)
         if not self.identity:
             return self.down(y, defer=self.defer_output)
-        # the identity experts' share, weight * input, joins the experts' sum in 32-bit
+        # the identity experts' share, weight * input, joins the experts' sum in 32-bit: in the consumer's kernel where it offers that
+        # (the block arrangement said so), else here
+        if self.leave_output_bias:
+            self.output_rows = (x, idw)
+            return self.down(y, defer=self.defer_output)
         return kernels.add_scaled_rows(self.down(y, out_dtype=torch.float32), x, idw)
 
     def _routed(self, x):

@@ -97,7 +97,7 @@ class LayerNorm(Norm):
         out = torch.empty((n, self.size), dtype=out_dtype or self.ctx.dtype, device=residual.device)
         if isinstance(delta, ChannelScaled):
             return kernels.layernorm(residual, self.weight, self.eps, out, delta=delta.y, delta_scale=scale, delta_weight=delta.weight.to(self.weight.dtype),
-                                     delta_bias=delta.bias, rows=rows, write_back=rows is None, center=self.center, bias=self.bias)
+                                     delta_bias=delta.bias, delta_rows=delta.rows, rows=rows, write_back=rows is None, center=self.center, bias=self.bias)
         terms = delta.terms if isinstance(delta, ScaledParts) else ([(delta, 1.0)] if delta is not None else [])
         if len(terms) > 2:
             raise ValueError(f"layer_norm: a weighted sum of {len(terms)} results (at most two)")
@@ -127,8 +127,8 @@ class ChannelScale(Norm):
     def bind(self, tensors):
         self.weight = tensors[self.weight_name].contiguous()
 
-    def defer(self, y, bias=None):
-        return ChannelScaled(y, self.weight, bias)
+    def defer(self, y, bias=None, rows=None):
+        return ChannelScaled(y, self.weight, bias, rows)
 
 
 @register_part("group_rms_norm")

@@ -308,12 +308,13 @@ def test_layer_norm_with_a_bias_adds_a_result_times_a_vector_along_the_row(dtype
         w, b, ls = ((0.3 * torch.randn(n, generator=g) + o).to(torch.bfloat16) for o in (1.0, 0.0, 0.6))
         ys = y.double().sum(0) if splits > 1 else y[0].to(dtype).double()
         db = 0.5 * torch.randn(n, generator=g) if rows % 2 else None          # the bias of the projection that made y, added ahead of the scale
-        want_h = h.double() + (ys + (db.double() if db is not None else 0.0)) * ls.double()
+        xr, rw = (torch.randn(rows, n, generator=g).to(dtype), torch.rand(rows, generator=g)) if rows % 3 else (None, None)    # a term with a weight a row
+        want_h = h.double() + (ys + (db.double() if db is not None else 0.0) + (rw.double()[:, None] * xr.double() if xr is not None else 0.0)) * ls.double()
         want_x = P.layer_norm(want_h, w.double(), b.double(), 1e-5)
         hd = h.cuda()
         out = torch.empty((rows, n), dtype=dtype, device="cuda")
         kernels.layernorm(hd, w.cuda(), 1e-5, out, delta=y.cuda() if splits > 1 else y[0].to(dtype).cuda(), delta_weight=ls.cuda(), bias=b.cuda(), write_back=True,
-                          delta_bias=db.cuda() if db is not None else None)
+                          delta_bias=db.cuda() if db is not None else None, delta_rows=(xr.cuda(), rw.cuda()) if xr is not None else None)
         assert torch.allclose(hd.cpu().double(), want_h, atol=3e-5, rtol=3e-6), (rows, n)
         assert torch.allclose(out.cpu().double(), want_x, atol=3e-5 if dtype == torch.float32 else 4e-2, rtol=1e-5 if dtype == torch.float32 else 1e-2)
         pick = torch.tensor([rows - 1, 0], dtype=torch.int32, device="cuda")           # the norm alone, of gathered rows; the stream stays
