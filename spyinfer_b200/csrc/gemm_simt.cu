@@ -73,8 +73,9 @@ gemm_simt_kernel(const TA* __restrict__ A, long long lda, const TW* __restrict__
 // under way at once, and the threads' sums are added in a fixed order.  A row's result does not depend on M either.
 constexpr int SKINNY_N = 32, SKINNY_NG = 16, SKINNY_THREADS = 256;
 
-// ROWS rows of A a block: with many rows every weight element a block fetches serves ROWS of them (each block reads all of W, so
-// with one row a block the weights cross the L2 once a row).  A row's sums are formed in the same order whatever ROWS is.
+// ROWS rows of A a block (every weight element a block fetches serves ROWS of them; a row's sums are formed in the same order
+// whatever ROWS is).  One row a block is what runs: four rows a block, tried for steps of many rows, were no faster (the weights of
+// a product this narrow stay in L1/L2, and the accumulators of four rows cost occupancy).
 template <typename TA, typename TW, typename TC, int ROWS>
 __global__ void __launch_bounds__(SKINNY_THREADS)
 gemm_skinny_kernel(const TA* __restrict__ A, long long lda, const TW* __restrict__ W, long long ldw, TC* __restrict__ C, long long ldc,
@@ -93,7 +94,7 @@ gemm_skinny_kernel(const TA* __restrict__ A, long long lda, const TW* __restrict
         for (int r = 0; r < ROWS; ++r)
 #pragma unroll
             for (int j = 0; j < SKINNY_NG; ++j) acc[r][j] = 0.f;
-#pragma unroll 4
+#pragma unroll(ROWS == 1 ? 4 : 2)
         for (int k = threadIdx.x; k < K; k += SKINNY_THREADS) {
             float av[ROWS];
 #pragma unroll
@@ -110,6 +111,7 @@ gemm_skinny_kernel(const TA* __restrict__ A, long long lda, const TW* __restrict
         for (int r = 0; r < ROWS; ++r)
 #pragma unroll
             for (int j = 0; j < SKINNY_NG; ++j) {
+                if (n0 + j >= N) break;                   // the same for every thread
                 const float sum = warp_sum(acc[r][j]);
                 if (lane == 0) part[r][warp][j] = sum;
             }
@@ -137,12 +139,8 @@ extern "C" int spy_gemm_simt(const void* A, int a_dtype, long long lda, const vo
         SPY_DISPATCH_DTYPE(a_dtype, TA, {
             SPY_DISPATCH_DTYPE(w_dtype, TW, {
                 SPY_DISPATCH_DTYPE(c_dtype, TC, {
-                    if (M >= 1024)
-                        spy_launch(gemm_skinny_kernel<TA, TW, TC, 4>, dim3((unsigned)((M + 3) / 4)), dim3(SKINNY_THREADS), 0, stream, (const TA*)A, lda,
-                                   (const TW*)W, ldw, (TC*)C, ldc, M, N, K);
-                    else
-                        spy_launch(gemm_skinny_kernel<TA, TW, TC, 1>, dim3((unsigned)M), dim3(SKINNY_THREADS), 0, stream, (const TA*)A, lda,
-                                   (const TW*)W, ldw, (TC*)C, ldc, M, N, K);
+                    spy_launch(gemm_skinny_kernel<TA, TW, TC, 1>, dim3((unsigned)M), dim3(SKINNY_THREADS), 0, stream, (const TA*)A, lda,
+                               (const TW*)W, ldw, (TC*)C, ldc, M, N, K);
                 })
             })
         })
