@@ -41,7 +41,10 @@ template <> struct Quad<bf16> {
 };
 
 // VEC: the row length is a multiple of 4 and every array is 16-byte aligned: four elements a load.
-template <typename TX, typename TD, typename TW, typename TO, bool VEC>
+// REG > 0 (with VEC): the row is exactly REG quads a thread (len == 4 * REG * blockDim.x) and stays in registers between the passes,
+// with all of a thread's loads under way together; REG == 0: any length, the row kept in shared memory.  The sums are formed in
+// the same order either way.
+template <typename TX, typename TD, typename TW, typename TO, bool VEC, int REG>
 __global__ void __launch_bounds__(1024)
 layernorm_kernel(TX* x, const TD* __restrict__ a, int a_splits, long long a_stride, float a_scale, const TD* __restrict__ b, int b_splits,
                  long long b_stride, float b_scale, const int* __restrict__ rows, const TW* __restrict__ w, TO* __restrict__ out, int len, float eps,
@@ -58,8 +61,9 @@ layernorm_kernel(TX* x, const TD* __restrict__ a, int a_splits, long long a_stri
     TO* orow = out + (size_t)blockIdx.x * len;
     constexpr int E = VEC ? 4 : 1;
     float sum = 0.f;
-    for (int i = threadIdx.x * E; i < len; i += blockDim.x * E) {
-        float v[4], d[4], p[4];
+    // the sum of everything that goes into the stream at elements i .. i + E - 1 (stored back when asked for)
+    const auto gather = [&](int i, float (&v)[4]) {
+        float d[4], p[4];
         if constexpr (VEC) Quad<TX>::load(xr + i, v); else v[0] = to_f32(xr[i]);
         if (ar) {
 #pragma unroll
@@ -102,13 +106,54 @@ layernorm_kernel(TX* x, const TD* __restrict__ a, int a_splits, long long a_stri
 #pragma unroll
             for (int e = 0; e < E; ++e) v[e] = fmaf(b_scale, d[e], v[e]);
         }
+        if (write_back) {
+            if constexpr (VEC) Quad<TX>::store(xr + i, v); else xr[i] = from_f32<TX>(v[0]);
+        }
+    };
+    // the normed elements i .. i + E - 1
+    const auto finish = [&](int i, const float (&v)[4], float mean, float inv) {
+        float wv[4], o[4];
+        if constexpr (VEC) Quad<TW>::load(w + i, wv); else wv[0] = to_f32(w[i]);
+#pragma unroll
+        for (int e = 0; e < E; ++e) o[e] = ((v[e] - mean) * inv) * wv[e];
+        if (bias) {
+            float bv[4];
+            if constexpr (VEC) Quad<TW>::load(bias + i, bv); else bv[0] = to_f32(bias[i]);
+#pragma unroll
+            for (int e = 0; e < E; ++e) o[e] += bv[e];
+        }
+        if constexpr (VEC) Quad<TO>::store(orow + i, o); else orow[i] = from_f32<TO>(o[0]);
+    };
+    if constexpr (REG > 0) {
+        float keep[REG][4];
+#pragma unroll
+        for (int q = 0; q < REG; ++q) gather((q * blockDim.x + threadIdx.x) * 4, keep[q]);
+#pragma unroll
+        for (int q = 0; q < REG; ++q)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) sum += keep[q][e];
+        const float mean = center ? block_sum(sum, scratch) / (float)len : 0.f;
+        float ss = 0.f;
+#pragma unroll
+        for (int q = 0; q < REG; ++q)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float dd = keep[q][e] - mean;
+                ss += dd * dd;
+            }
+        ss = block_sum(ss, scratch);
+        const float inv = 1.0f / sqrtf(ss / (float)len + eps);
+#pragma unroll
+        for (int q = 0; q < REG; ++q) finish((q * blockDim.x + threadIdx.x) * 4, keep[q], mean, inv);
+        return;
+    }
+    for (int i = threadIdx.x * E; i < len; i += blockDim.x * E) {
+        float v[4];
+        gather(i, v);
 #pragma unroll
         for (int e = 0; e < E; ++e) {
             row_buf[i + e] = v[e];
             sum += v[e];
-        }
-        if (write_back) {
-            if constexpr (VEC) Quad<TX>::store(xr + i, v); else xr[i] = from_f32<TX>(v[0]);
         }
     }
     const float mean = center ? block_sum(sum, scratch) / (float)len : 0.f;
@@ -123,17 +168,10 @@ layernorm_kernel(TX* x, const TD* __restrict__ a, int a_splits, long long a_stri
     ss = block_sum(ss, scratch);
     const float inv = 1.0f / sqrtf(ss / (float)len + eps);
     for (int i = threadIdx.x * E; i < len; i += blockDim.x * E) {
-        float wv[4], o[4];
-        if constexpr (VEC) Quad<TW>::load(w + i, wv); else wv[0] = to_f32(w[i]);
+        float v[4];
 #pragma unroll
-        for (int e = 0; e < E; ++e) o[e] = ((row_buf[i + e] - mean) * inv) * wv[e];
-        if (bias) {
-            float bv[4];
-            if constexpr (VEC) Quad<TW>::load(bias + i, bv); else bv[0] = to_f32(bias[i]);
-#pragma unroll
-            for (int e = 0; e < E; ++e) o[e] += bv[e];
-        }
-        if constexpr (VEC) Quad<TO>::store(orow + i, o); else orow[i] = from_f32<TO>(o[0]);
+        for (int e = 0; e < E; ++e) v[e] = row_buf[i + e];
+        finish(i, v, mean, inv);
     }
 }
 
@@ -162,7 +200,11 @@ static int run_layernorm(void* x, int x_dtype, const void* a, int a_splits, long
         SPY_DISPATCH_DTYPE(delta_dtype, TD, {
             SPY_DISPATCH_DTYPE(w_dtype, TW, {
                 SPY_DISPATCH_DTYPE(out_dtype, TO, {
-                    auto kernel = vec ? layernorm_kernel<TX, TD, TW, TO, true> : layernorm_kernel<TX, TD, TW, TO, false>;
+                    // rows of exactly one, two or four quads a thread stay in registers
+                    const int reg = !vec ? 0 : (len == 4 * threads ? 1 : (len == 8 * threads ? 2 : (len == 16 * threads ? 4 : 0)));
+                    auto kernel = reg == 1 ? layernorm_kernel<TX, TD, TW, TO, true, 1> : reg == 2 ? layernorm_kernel<TX, TD, TW, TO, true, 2>
+                                : reg == 4 ? layernorm_kernel<TX, TD, TW, TO, true, 4>
+                                : (vec ? layernorm_kernel<TX, TD, TW, TO, true, 0> : layernorm_kernel<TX, TD, TW, TO, false, 0>);
                     if (smem > 48 * 1024) SPY_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
                     spy_launch(kernel, dim3(n), dim3(threads), smem, stream, (TX*)x, (const TD*)a, a_splits, a_stride, a_scale, (const TD*)b, b_splits,
                                b_stride, b_scale, rows, (const TW*)w, (TO*)out, len, eps, write_back, center, (const TW*)bias, (const TW*)a_w, a_bias, (const TO*)a_rows, a_row_w);
