@@ -26,6 +26,7 @@ struct MoeRouting {
     int group_count, group_keep;   // 0: no groups
     int act;                       // 0: clamped g * sigmoid(alpha g) * (u + 1); 1: silu(g) * u
     float* id_weight;              // null, or [T]: the sum of the chosen identity experts' weights
+    float* shared_weight;          // null, or [T]: the shared expert's weight (sigmoid of its gate's logit)
 };
 
 template <typename TA, typename TO>
@@ -93,8 +94,10 @@ __global__ void moe_activation_kernel(const TA* __restrict__ gu, long long gu_ld
         for (int e = experts; e < total; ++e) idw += kept_w[e];
         r.id_weight[t] = idw;
     }
+    if (r.shared_weight != nullptr && tid == 0) r.shared_weight[t] = w_s[total];
     if (weights_out != nullptr)
         for (int e = tid; e <= total; e += blockDim.x) weights_out[(long long)t * (total + 1) + e] = e < total ? kept_w[e] : w_s[total];
+    if (gu == nullptr) return;                   // the weights alone were asked for
     const TA* g_row = gu + (long long)t * gu_ld;
     TO* y_row = y + (long long)t * y_ld;
     const int routed = experts * ff;
@@ -183,18 +186,20 @@ extern "C" int spy_moe_activation(const void* gu, int gu_dtype, long long gu_ld,
                                   long long y_ld, int tokens, int experts, int top, int ff, float limit, int shared_ff, float shared_limit, float alpha,
                                   float* weights_out, cudaStream_t stream)
 {
-    MoeRouting r = {0, nullptr, 0, 0, 0, nullptr};
+    MoeRouting r = {0, nullptr, 0, 0, 0, nullptr, nullptr};
     return run_moe_activation(gu, gu_dtype, gu_ld, logits, logits_ld, y, y_dtype, y_ld, tokens, experts, top, ff, limit, shared_ff, shared_limit, alpha,
                               weights_out, r, stream);
 }
 
 // The same with the routing's options (see the head of this file); logits hold experts + identity columns, then the shared gate's.
+// gu null (y then unused): the routing alone, its weights into weights_out, id_weight and shared_weight.
 extern "C" int spy_moe_activation_routed(const void* gu, int gu_dtype, long long gu_ld, const float* logits, long long logits_ld, void* y, int y_dtype,
                                          long long y_ld, int tokens, int experts, int top, int ff, float limit, int shared_ff, float shared_limit,
                                          float alpha, float* weights_out, int identity, const float* correction, int group_count, int group_keep, int act,
-                                         float* id_weight, cudaStream_t stream)
+                                         float* id_weight, float* shared_weight, cudaStream_t stream)
 {
-    MoeRouting r = {identity, correction, group_count, group_keep, act, id_weight};
+    if (gu == nullptr && weights_out == nullptr) SPY_FAIL("moe_activation: neither activations nor weights are asked for");
+    MoeRouting r = {identity, correction, group_count, group_keep, act, id_weight, shared_weight};
     return run_moe_activation(gu, gu_dtype, gu_ld, logits, logits_ld, y, y_dtype, y_ld, tokens, experts, top, ff, limit, shared_ff, shared_limit, alpha,
                               weights_out, r, stream);
 }
@@ -350,7 +355,7 @@ __global__ void gather_rows_kernel(const uint8_t* __restrict__ in, const int* __
 // y[r, i] = w[r] * g * sigmoid(alpha g) * (u + 1) over rows of [gate (ff) | up (ff)], g = min(gate, limit), u = clamp(up, -limit, limit)
 template <typename TA, typename TO>
 __global__ void expert_activation_kernel(const TA* __restrict__ gu, long long gu_ld, const float* __restrict__ row_w, TO* __restrict__ y, long long y_ld,
-                                         int ff, float limit, float alpha, int vec)
+                                         int ff, float limit, float alpha, int vec, int act)
 {
     pdl_enter();
     const long long r = blockIdx.x;
@@ -367,6 +372,11 @@ __global__ void expert_activation_kernel(const TA* __restrict__ gu, long long gu
                 __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&packed);
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
+                    if (act == 1) {
+                        const float ga = __low2float(g2[q]), gb = __high2float(g2[q]);
+                        o2[q] = __floats2bfloat162_rn(w * (ga / (1.0f + expf(-ga))) * __low2float(u2[q]), w * (gb / (1.0f + expf(-gb))) * __high2float(u2[q]));
+                        continue;
+                    }
                     const float ga = fminf(__low2float(g2[q]), limit), gb = fminf(__high2float(g2[q]), limit);
                     const float ua = fminf(fmaxf(__low2float(u2[q]), -limit), limit), ub = fminf(fmaxf(__high2float(u2[q]), -limit), limit);
                     o2[q] = __floats2bfloat162_rn(w * (ga / (1.0f + expf(-alpha * ga))) * (ua + 1.0f), w * (gb / (1.0f + expf(-alpha * gb))) * (ub + 1.0f));
@@ -377,6 +387,11 @@ __global__ void expert_activation_kernel(const TA* __restrict__ gu, long long gu
         }
     }
     for (int i = threadIdx.x; i < ff; i += blockDim.x) {
+        if (act == 1) {
+            const float g = to_f32(src[i]);
+            dst[i] = from_f32<TO>(w * (g / (1.0f + expf(-g))) * to_f32(src[ff + i]));
+            continue;
+        }
         const float g = fminf(to_f32(src[i]), limit);
         const float u = fminf(fmaxf(to_f32(src[ff + i]), -limit), limit);
         dst[i] = from_f32<TO>(w * (g / (1.0f + expf(-alpha * g))) * (u + 1.0f));
@@ -391,7 +406,10 @@ __global__ void moe_combine_kernel(const TR* __restrict__ rows, const int* __res
     const long long t = blockIdx.x;
     for (int i = threadIdx.x; i < len; i += blockDim.x) {
         float acc = 0.f;
-        for (int k = 0; k < top; ++k) acc += to_f32(rows[(long long)slot[t * top + k] * len + i]);
+        for (int k = 0; k < top; ++k) {
+            const int r = slot[t * top + k];         // below 0: the pair has no row (fewer experts than `top` were chosen)
+            if (r >= 0) acc += to_f32(rows[(long long)r * len + i]);
+        }
         if (shared != nullptr) acc += to_f32(shared[t * len + i]);
         out[t * len + i] = acc;
     }
@@ -414,6 +432,62 @@ extern "C" int spy_moe_route(const float* logits, long long logits_ld, int token
     return 0;
 }
 
+// The (token, chosen expert) pairs of a step from a matrix of routing weights [tokens, ld] whose entry is the expert's weight where
+// the token chose it and 0 elsewhere (what moe_activation leaves in weights_out): a token's chosen experts in ascending order, at
+// most `top` of them; pairs beyond a token's last have the expert -1, weight 0 and no row.  One warp a token.
+__global__ void moe_pairs_kernel(const float* __restrict__ weights, long long ld, int tokens, int experts, int top, int* __restrict__ choice,
+                                 float* __restrict__ choice_w, int* __restrict__ slot, int* __restrict__ counts)
+{
+    extern __shared__ int hist_s[];
+    pdl_enter();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) hist_s[e] = 0;
+    __syncthreads();
+    for (long long t = (long long)blockIdx.x * nwarps + warp; t < tokens; t += (long long)gridDim.x * nwarps) {
+        const float* w = weights + t * ld;
+        int k_base = 0;
+        for (int e0 = 0; e0 < experts; e0 += 32) {
+            const int e = e0 + lane;
+            const float v = e < experts ? w[e] : 0.f;
+            const bool chosen = v != 0.f;
+            const unsigned ballot = __ballot_sync(0xffffffffu, chosen);
+            const int k = k_base + __popc(ballot & ((1u << lane) - 1u));
+            if (chosen && k < top) {
+                choice[t * top + k] = e;
+                choice_w[t * top + k] = v;
+                atomicAdd(hist_s + e, 1);
+            }
+            k_base += __popc(ballot);
+        }
+        for (int k = min(k_base, top) + lane; k < top; k += 32) {
+            choice[t * top + k] = -1;
+            choice_w[t * top + k] = 0.f;
+        }
+        for (int k = lane; k < top; k += 32) slot[t * top + k] = -1;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < experts; e += blockDim.x)
+        if (hist_s[e] != 0) atomicAdd(counts + e, hist_s[e]);
+}
+
+// weights [tokens, ld] float32 (the first `experts` columns are looked at); the other arrays as for spy_moe_route.
+extern "C" int spy_moe_route_weights(const float* weights, long long ld, int tokens, int experts, int top, int* choice, float* choice_w, int* counts,
+                                     int* offsets, int* slot, int* row_token, float* row_w, cudaStream_t stream)
+{
+    if (tokens <= 0) return 0;
+    if (experts <= 0 || experts > MOE_MAX_EXPERTS || top <= 0) SPY_FAIL("moe_route_weights: %d experts (at most %d), top %d", experts, MOE_MAX_EXPERTS, top);
+    SPY_CUDA(cudaMemsetAsync(counts, 0, sizeof(int) * experts, stream));
+    const int warps = 4;
+    const int blocks = min((tokens + warps - 1) / warps, 4 * 148);
+    spy_launch_in_order(moe_pairs_kernel, dim3(blocks), dim3(32 * warps), (size_t)experts * sizeof(int), stream, weights, ld, tokens, experts, top, choice,
+                        choice_w, slot, counts);
+    SPY_CHECK_LAUNCH("moe_pairs");
+    spy_launch(moe_slots_kernel, dim3(experts), dim3(1024), 0, stream, (const int*)choice, (const float*)choice_w, (const int*)counts,
+               tokens * top, top, experts, offsets, slot, row_token, row_w);
+    SPY_CHECK_LAUNCH("moe_slots");
+    return 0;
+}
+
 extern "C" int spy_gather_rows(const void* in, const int* row_token, void* out, int rows, long long row_bytes, cudaStream_t stream)
 {
     if (rows <= 0 || row_bytes <= 0) return 0;
@@ -422,15 +496,17 @@ extern "C" int spy_gather_rows(const void* in, const int* row_token, void* out, 
     return 0;
 }
 
+// act: 0 the clamped form above, 1 w * silu(gate) * up without clamps
 extern "C" int spy_expert_activation(const void* gu, int gu_dtype, long long gu_ld, const float* row_w, void* y, int y_dtype, long long y_ld, int rows, int ff,
-                                     float limit, float alpha, cudaStream_t stream)
+                                     float limit, float alpha, cudaStream_t stream, int act)
 {
     if (rows <= 0 || ff <= 0) return 0;
+    if (act < 0 || act > 1) SPY_FAIL("expert_activation: activation code %d", act);
     const int vec = gu_dtype == SPY_BF16 && y_dtype == SPY_BF16 && ff % 8 == 0 && gu_ld % 8 == 0 && y_ld % 8 == 0
                     && ((reinterpret_cast<uintptr_t>(gu) | reinterpret_cast<uintptr_t>(y)) & 15) == 0;
     SPY_DISPATCH_DTYPE(gu_dtype, TA, {
         SPY_DISPATCH_DTYPE(y_dtype, TO, {
-            spy_launch(expert_activation_kernel<TA, TO>, dim3(rows), dim3(256), 0, stream, (const TA*)gu, gu_ld, row_w, (TO*)y, y_ld, ff, limit, alpha, vec);
+            spy_launch(expert_activation_kernel<TA, TO>, dim3(rows), dim3(256), 0, stream, (const TA*)gu, gu_ld, row_w, (TO*)y, y_ld, ff, limit, alpha, vec, act);
         })
     })
     SPY_CHECK_LAUNCH("expert_activation");

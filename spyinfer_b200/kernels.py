@@ -1354,8 +1354,33 @@ def moe_activation(gate_up: torch.Tensor, logits: torch.Tensor, out: torch.Tenso
     else:
         count, keep = (int(groups[0]), int(groups[1])) if groups else (0, 0)
         _call("moe", "spy_moe_activation_routed", *args, int(identity), _ptr(correction), count, keep, 1 if activation == "silu" else 0, _ptr(id_weight),
-              _stream())
+              None, _stream())
     return out
+
+
+def moe_route_general(logits: torch.Tensor, experts: int, top: int, identity: int = 0, correction: Optional[torch.Tensor] = None,
+                      groups: Optional[tuple] = None, has_shared: bool = False):
+    """As ``moe_route`` for a choice with the options of ``moe_activation`` (identity experts, correction, groups): the (token,
+    chosen real expert) pairs of a step sorted by expert.  Returns ``offsets [experts + 1]``, ``slot [T, top]`` (the row of each
+    pair, -1 where a token chose fewer real experts than ``top``), ``row_token``, ``row_w`` (``[T top]``, the first ``offsets[-1]``
+    rows count), ``shared_w [T]`` or None, and ``id_weight [T]`` (the chosen identity experts' summed weights) or None."""
+    _check(logits, "router logits", torch.float32, 2)
+    T, total, dev = logits.shape[0], experts + int(identity), logits.device
+    if logits.shape[1] < total + (1 if has_shared else 0):
+        raise KernelError("moe_route_general: the logits lack columns")
+    weights = torch.empty((T, total + 1), dtype=torch.float32, device=dev)
+    floats = torch.empty((2 * T * top + 2 * T,), dtype=torch.float32, device=dev)
+    choice_w, row_w, shared_w, idw = floats[:T * top], floats[T * top:2 * T * top], floats[2 * T * top:2 * T * top + T], floats[2 * T * top + T:]
+    count, keep = (int(groups[0]), int(groups[1])) if groups else (0, 0)
+    _call("moe", "spy_moe_activation_routed", None, BF16, ctypes.c_longlong(0), _ptr(logits), ctypes.c_longlong(logits.shape[1]), None, BF16,
+          ctypes.c_longlong(0), T, int(experts), int(top), 1, ctypes.c_float(0.0), 1 if has_shared else 0, ctypes.c_float(0.0), ctypes.c_float(0.0),
+          _ptr(weights), int(identity), _ptr(correction), count, keep, 1, _ptr(idw if identity else None), _ptr(shared_w if has_shared else None), _stream())
+    ints = torch.empty((3 * T * top + 2 * experts + 1,), dtype=torch.int32, device=dev)
+    choice, slot, row_token = ints[:T * top], ints[T * top:2 * T * top], ints[2 * T * top:3 * T * top]
+    counts, offsets = ints[3 * T * top:3 * T * top + experts], ints[3 * T * top + experts:]
+    _call("moe", "spy_moe_route_weights", _ptr(weights), ctypes.c_longlong(total + 1), T, int(experts), int(top), _ptr(choice), _ptr(choice_w), _ptr(counts),
+          _ptr(offsets), _ptr(slot), _ptr(row_token), _ptr(row_w), _stream())
+    return offsets, slot.view(T, top), row_token, row_w, (shared_w if has_shared else None), (idw if identity else None)
 
 
 def add_scaled_rows(out: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
@@ -1462,8 +1487,10 @@ def gather_rows(x: torch.Tensor, row_token: torch.Tensor, out: torch.Tensor) -> 
     return out
 
 
-def expert_activation(gate_up: torch.Tensor, row_w: torch.Tensor, out: torch.Tensor, limit: float, alpha: float = 1.702) -> torch.Tensor:
-    """``out[r] = row_w[r] * g * sigmoid(alpha g) * (u + 1)`` over rows ``[gate | up]`` with ``g = min(gate, limit)``, ``u = clamp(up, -limit, limit)``."""
+def expert_activation(gate_up: torch.Tensor, row_w: torch.Tensor, out: torch.Tensor, limit: float, alpha: float = 1.702,
+                      activation: str = "clamped_swish") -> torch.Tensor:
+    """``out[r] = row_w[r] * g * sigmoid(alpha g) * (u + 1)`` over rows ``[gate | up]`` with ``g = min(gate, limit)``, ``u = clamp(up, -limit, limit)``;
+    ``activation="silu"``: ``row_w[r] * silu(gate) * up`` without clamps."""
     _check(gate_up, "expert gate|up", ndim=2)
     _check(out, "expert activations", ndim=2)
     _check(row_w, "row weights", torch.float32, 1)
@@ -1471,7 +1498,8 @@ def expert_activation(gate_up: torch.Tensor, row_w: torch.Tensor, out: torch.Ten
     if two % 2 or tuple(out.shape) != (R, two // 2) or row_w.shape[0] < R:
         raise KernelError("expert_activation: shapes do not fit")
     _call("moe", "spy_expert_activation", _ptr(gate_up), _code(gate_up, "expert gate|up"), ctypes.c_longlong(two), _ptr(row_w), _ptr(out),
-          _code(out, "expert activations"), ctypes.c_longlong(two // 2), R, two // 2, ctypes.c_float(limit), ctypes.c_float(alpha), _stream())
+          _code(out, "expert activations"), ctypes.c_longlong(two // 2), R, two // 2, ctypes.c_float(limit), ctypes.c_float(alpha), _stream(),
+          1 if activation == "silu" else 0)
     return out
 
 

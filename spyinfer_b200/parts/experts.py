@@ -105,7 +105,7 @@ class ExpertMixture(FeedForward):
         return [self.router, self.gate_up, self.down]
 
     def forward(self, x):
-        if self.plain_choice and 0 < self.routed_from <= x.shape[0] and self.top < self.experts and not torch.cuda.is_current_stream_capturing():
+        if 0 < self.routed_from <= x.shape[0] and self.top < self.outputs and not torch.cuda.is_current_stream_capturing():
             return self._routed(x)
         logits = self.router(x, out_dtype=torch.float32)
         gu = self.gate_up(x)
@@ -128,24 +128,36 @@ class ExpertMixture(FeedForward):
     def _routed(self, x):
         T, E, top, ff, sff, dev = x.shape[0], self.experts, self.top, self.ff, self.shared_ff, x.device
         logits = self.router(x, out_dtype=torch.float32)
-        offsets, slot, row_token, row_w, shared_w = kernels.moe_route(logits, E, top, bool(sff))
+        idw = None
+        if self.plain_choice:
+            offsets, slot, row_token, row_w, shared_w = kernels.moe_route(logits, E, top, bool(sff))
+        else:
+            offsets, slot, row_token, row_w, shared_w, idw = kernels.moe_route_general(logits, E, top, self.identity, self.correction, self.groups, bool(sff))
         starts = offsets.cpu().tolist()                      # the layer's one read-back: the experts' row counts size their products
-        R = T * top
-        rows = kernels.gather_rows(x, row_token, torch.empty((R, self.hidden), dtype=x.dtype, device=dev))
-        gu = torch.empty((R, 2 * ff), dtype=self.ctx.dtype, device=dev)
-        for e in range(E):
-            a, b = starts[e], starts[e + 1]
-            if b > a:
-                self.gate_up.part(rows[a:b], rows=(2 * ff * e, 2 * ff * (e + 1)), out=gu[a:b])
-        y = kernels.expert_activation(gu, row_w, torch.empty((R, ff), dtype=self.ctx.dtype, device=dev), self.limit, self.slope)
+        R, n = T * top, starts[E]                            # n rows are in use: a token may have chosen fewer real experts than `top`
         results = torch.empty((R, self.hidden), dtype=torch.float32, device=dev)
-        for e in range(E):
-            a, b = starts[e], starts[e + 1]
-            if b > a:
-                self.down.part(y[a:b], cols=(ff * e, ff * (e + 1)), out=results[a:b])
+        if n:
+            rows = kernels.gather_rows(x, row_token[:n], torch.empty((n, self.hidden), dtype=x.dtype, device=dev))
+            gu = torch.empty((n, 2 * ff), dtype=self.ctx.dtype, device=dev)
+            for e in range(E):
+                a, b = starts[e], starts[e + 1]
+                if b > a:
+                    self.gate_up.part(rows[a:b], rows=(2 * ff * e, 2 * ff * (e + 1)), out=gu[a:b])
+            y = kernels.expert_activation(gu, row_w, torch.empty((n, ff), dtype=self.ctx.dtype, device=dev), self.limit, self.slope, activation=self.activation)
+            for e in range(E):
+                a, b = starts[e], starts[e + 1]
+                if b > a:
+                    self.down.part(y[a:b], cols=(ff * e, ff * (e + 1)), out=results[a:b])
         shared = None
         if sff:
             sgu = self.gate_up.part(x, rows=(2 * ff * E, 2 * ff * E + 2 * sff), out_dtype=self.ctx.dtype)
-            sy = kernels.expert_activation(sgu, shared_w, torch.empty((T, sff), dtype=self.ctx.dtype, device=dev), self.shared_limit, self.slope)
+            sy = kernels.expert_activation(sgu, shared_w, torch.empty((T, sff), dtype=self.ctx.dtype, device=dev), self.shared_limit, self.slope,
+                                           activation=self.activation)
             shared = self.down.part(sy, cols=(ff * E, ff * E + sff), out_dtype=torch.float32)
-        return kernels.moe_combine(results, slot, shared, torch.empty((T, self.hidden), dtype=torch.float32, device=dev))
+        out = kernels.moe_combine(results, slot, shared, torch.empty((T, self.hidden), dtype=torch.float32, device=dev))
+        if idw is None:
+            return out
+        if self.leave_output_bias:                           # the identity experts' share is the consumer's to add
+            self.output_rows = (x, idw)
+            return out
+        return kernels.add_scaled_rows(out, x, idw)

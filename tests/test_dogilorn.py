@@ -772,3 +772,69 @@ def test_greedy_generation_through_the_engine_and_its_scheduler(models, name):
             toks.append(int(logits.argmax()))
             assert out[i] == toks[-1], (i, out, toks[len(prompt):])
     assert engine.stats()["free_slots"] == 3
+
+
+# ---- the routed form of the expert mixture ----------------------------------------------------------------
+
+@gpu
+@pytest.mark.parametrize("experts,identity,top,groups,shared", [(6, 2, 3, (4, 2), True), (5, 0, 1, None, False), (13, 3, 4, (4, 2), True), (2, 2, 2, (2, 2), False),
+                                                                (60, 4, 6, (8, 3), False)])
+def test_pairs_of_token_and_chosen_real_expert_sorted_by_expert(experts, identity, top, groups, shared):
+    """The sorted pairs of the general choice: every real expert's run of rows holds exactly the tokens that chose it, in their
+    order, with the plain scores as weights; identity experts take no rows (their weights are summed a token); a token that
+    chose fewer real experts than ``top`` has pairs without a row."""
+    from spyinfer_b200 import kernels
+
+    g = torch.Generator().manual_seed(experts + top)
+    T, total = 300, experts + identity
+    logits = torch.randn(T, total + (1 if shared else 0), generator=g) * 1.5
+    corr = torch.randn(total, generator=g) * 0.1
+    mlp = {"router": {"experts": experts, "identity": identity, "top": top}}
+    if groups:
+        mlp["router"]["groups"] = {"count": groups[0], "keep": groups[1]}
+    idx, w = P.route(logits[:, :total].double(), mlp, {"router": torch.eye(total, dtype=P.F), "correction": corr.double()}, "")
+    offsets, slot, row_token, row_w, shared_w, idw = kernels.moe_route_general(logits.cuda(), experts, top, identity, corr.cuda(), groups, shared)
+    offsets, slot, row_token, row_w = offsets.cpu().tolist(), slot.cpu(), row_token.cpu(), row_w.cpu()
+    want_rows = {e: [] for e in range(experts)}
+    for t in range(T):
+        for e, wt in sorted(zip(idx[t].tolist(), w[t].tolist())):
+            if e < experts:
+                want_rows[e].append((t, wt))
+    assert offsets[0] == 0 and [offsets[e + 1] - offsets[e] for e in range(experts)] == [len(want_rows[e]) for e in range(experts)]
+    for e in range(experts):
+        got = [(int(row_token[r]), float(row_w[r])) for r in range(offsets[e], offsets[e + 1])]
+        assert [t for t, _ in got] == [t for t, _ in want_rows[e]]
+        assert np.allclose([x for _, x in got], [x for _, x in want_rows[e]], atol=1e-6)
+    n = offsets[experts]
+    for t in range(T):
+        real = sorted(e for e in idx[t].tolist() if e < experts)
+        rows = slot[t].tolist()
+        assert all(r >= 0 for r in rows[:len(real)]) and all(r < 0 for r in rows[len(real):])
+        assert [next(e for e in range(experts) if offsets[e] <= r < offsets[e + 1]) for r in rows[:len(real)]] == real and all(r < n for r in rows)
+    if identity:
+        want_id = torch.zeros(T, total, dtype=P.F).scatter_(1, idx, w)[:, experts:].sum(1)
+        assert torch.allclose(idw.cpu().double(), want_id, atol=1e-6)
+    if shared:
+        assert torch.allclose(shared_w.cpu().double(), torch.sigmoid(logits[:, total].double()), atol=1e-6)
+
+
+@gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["a", "b", "c", "d", "e", "f"])
+def test_the_routed_mixture_agrees_with_the_plain_model_and_with_the_dense_form(models, name, dtype, monkeypatch):
+    """Steps of eight tokens or more take the routed form (each expert's products on its own rows), shorter ones and decoding the
+    dense one; both agree with the plain model, and in float32 with each other to rounding."""
+    toks = tokens_of(name, 150, salt=8)
+    want = plain_logits(name, models, toks)
+    dense = run_cuts(make_runner(models[name][0], dtype), "w", toks, [150])
+    monkeypatch.setenv("SPYINFER_MOE_ROUTED_FROM", "8")
+    runner = make_runner(models[name][0], dtype)
+    mixtures = [l.feed_forward for l in runner.model.layers if getattr(l.feed_forward, "routed_from", None) is not None]
+    assert mixtures and all(m.routed_from == 8 for m in mixtures)
+    whole = run_cuts(runner, "w", toks, [150])
+    agrees(whole, want, dtype, "routed, whole")
+    portions = run_cuts(runner, "p", toks, cycle_cuts(150, [2, 31, 8, 3, 64, 9]))
+    agrees(portions, want, dtype, "routed and dense portions")
+    if dtype == "float32":
+        scale = np.abs(dense).max()
+        assert np.abs(whole - dense).max() / scale < 4e-6 and np.abs(portions - dense).max() / scale < 4e-6
