@@ -15,7 +15,8 @@ off; never inside a captured graph) takes the routed form instead: the (token, c
 device, the tokens' rows gathered in that order, each expert's two products run on its own run of rows (views of the same
 fused weights, nothing stored twice), and every token's ``top`` results and the shared expert's are added in a fixed order in
 32-bit.  The experts' row counts are read back once a layer to size the products.  Weights and arithmetic are the same, so the
-two forms differ by the order of sums only.
+two forms differ by the order of sums only.  Both forms serve the options of the choice (a correction for the choice only, groups
+of router outputs, identity experts, whose pairs take no rows) and both activations.
 """
 from __future__ import annotations
 
