@@ -838,3 +838,75 @@ def test_the_routed_mixture_agrees_with_the_plain_model_and_with_the_dense_form(
     if dtype == "float32":
         scale = np.abs(dense).max()
         assert np.abs(whole - dense).max() / scale < 4e-6 and np.abs(portions - dense).max() / scale < 4e-6
+
+
+# ---- configurations drawn at random -------------------------------------------------------------------------
+
+def random_config(rng):
+    """A configuration with every size, option and layer order drawn at random (tensor-core sizes and others, readers of earlier
+    layers' keys, masks from one token to longer than the sequence, every kind of feed-forward and choice)."""
+    cfg = {"architecture": "Dogilorn", "vocab": rng.randrange(50, 600), "width": rng.choice([64, 96, 128, 160, 192, 256, 320]),
+           "norm": {"eps": rng.choice([1e-5, 1e-6])}}
+    if rng.random() < 0.85:
+        cfg["canon"] = {"taps": rng.choice([1, 2, 3, 4, 4, 6, 8])}
+    if rng.random() < 0.85:
+        cfg["embedding"] = {"scale": rng.choice([1.0, 2.0, 3.0, 0.5, 7.5])}
+    layers, owners = [], []
+    for i in range(rng.randrange(2, 9)):
+        if owners and rng.random() < 0.4:                        # a reader of an earlier layer's keys and values, with a scale of its own
+            j = rng.choice(owners)
+            m = dict(layers[j]["mixer"], kv_from=j, scale=rng.choice([0.1, 0.2, layers[j]["mixer"]["dim"] ** -0.5]))
+        else:
+            heads = rng.choice([1, 2, 4, 8, 16, 3, 6, 20, 32])
+            dim = rng.choice([8, 16, 32, 64, 128, 24, 48, 192, 10, 256])
+            m = {"heads": heads, "kv_heads": rng.choice([d for d in range(1, heads + 1) if heads % d == 0]), "dim": dim,
+                 "vdim": rng.choice([8, 16, 32, 64, 128, 40, dim, dim]), "scale": rng.choice([dim ** -0.5, 0.13, 0.3])}
+            if rng.random() < 0.85:
+                m["rot"] = {"base": rng.choice([10000.0, 500000.0, 100.0]), "dims": rng.choice(range(2, dim + 1, 2))}
+            owners.append(i)
+        m["mask"] = {"size": rng.choice([1, 5, 16, 17, 33, 64, 100, 200, 1000]), "keep_first": rng.choice([0, 1, 2, 4, 4, 8, 16, 17, 40])}
+        kind = rng.random()
+        if kind < 0.1:
+            mlp = None
+        elif kind < 0.55:
+            mlp = _dense(rng.choice([32, 64, 96, 320, 100, 52]), rng.choice([1.0, 0.5, 2.0, 7.0]))
+        else:
+            while True:
+                experts, identity = rng.randrange(1, 17), rng.randrange(0, 5)
+                total = experts + identity
+                top, groups = rng.randrange(1, min(total, 6) + 1), None
+                if rng.random() < 0.7:
+                    count = rng.choice([c for c in range(1, total + 1) if total % c == 0])
+                    keeps = [k for k in range(1, count + 1) if k * (total // count) >= top]
+                    if not keeps:
+                        continue
+                    groups = (count, rng.choice(keeps))
+                break
+            mlp = _moe(experts, identity, top, rng.choice([16, 32, 64, 24, 12]), groups=groups, shared=rng.choice([32, 96, 40]) if rng.random() < 0.7 else None)
+        layers.append({"type": "attention", "mixer": m, "mlp": mlp})
+    cfg["layers"] = layers
+    return cfg
+
+
+@gpu
+@pytest.mark.parametrize("seed", [3, 11, 19, 27, 42, 58, 77, 91])
+def test_configurations_drawn_at_random_agree_with_the_plain_model_in_every_cut(tmp_path, seed):
+    """Whole, the last 60 tokens one by one, and portions down to two tokens, in both formats; in float32 the cuts agree with each
+    other to rounding."""
+    rng = random.Random(seed)
+    cfg = random_config(rng)
+    w = P.random_weights(cfg, seed)
+    model_dir = write_model(tmp_path, cfg, w)
+    n = 330
+    toks = [rng.randrange(cfg["vocab"]) for _ in range(n)]
+    want = P.forward(cfg, P.as_float64(w), toks).numpy()
+    for dtype in ("float32", "bfloat16"):
+        runner = make_runner(model_dir, dtype, page_size=16, num_pages=64)
+        whole = run_cuts(runner, "w", toks, [n])
+        one_by_one = run_cuts(runner, "d", toks, [n - 60] + [1] * 60)
+        portions = run_cuts(runner, "p", toks, cycle_cuts(n, [2, 3, 2, 17, 2, 5, 31, 2, 64, 129]))
+        for what, got in (("whole", whole), ("decoded", one_by_one), ("portions", portions)):
+            agrees(got, want, dtype, f"{json.dumps(cfg)}: {what}")
+        if dtype == "float32":
+            scale = np.abs(whole).max()
+            assert np.abs(one_by_one - whole).max() / scale < 4e-6 and np.abs(portions - whole).max() / scale < 4e-6
